@@ -1,0 +1,185 @@
+/*
+ * b200tp — C ABI of the B200 (sm_100a) tensor-parallel layer path for nano-vllm.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream handle
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream) and
+ * returns an int status (B2_OK = 0).  Nothing here allocates, synchronises or
+ * creates streams inside a compute call, so calls may be captured in CUDA
+ * graphs.  All activations and weights are bf16 (16-bit words, row-major, the
+ * innermost dimension contiguous) unless stated otherwise.  PyTorch (or any
+ * caller) owns every tensor passed in; the library owns only what
+ * b2_ctx_create allocates.
+ *
+ * Citations name the reference lines (nano-vllm, path within the project)
+ * whose behaviour the entry point reproduces.
+ */
+#ifndef B200TP_H
+#define B200TP_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  B2_OK = 0,
+  B2_ERR_ARG = 1,         /* null pointer, bad alignment, negative size            */
+  B2_ERR_SHAPE = 2,       /* a size outside what the context was created for       */
+  B2_ERR_CUDA = 3,        /* a CUDA runtime/driver call failed (see b2_last_error) */
+  B2_ERR_STATE = 4,       /* peers not imported, context destroyed, ...            */
+  B2_ERR_TIMEOUT = 5,     /* a bounded device-side wait ran out (from b2_status)   */
+  B2_ERR_UNSUPPORTED = 6
+};
+
+#define B2_HANDLE_BYTES 64 /* one exported symmetric-memory handle */
+
+typedef struct b2_ctx b2_ctx;
+
+typedef struct b2_config {
+  int rank;            /* tensor-parallel rank of this process                         */
+  int world;           /* tensor-parallel size (1, 2, 4 or 8)                          */
+  int device;          /* CUDA device ordinal of this process                          */
+  int max_tokens;      /* largest token count M of any call (prefill budget)           */
+  int hidden;          /* largest row length N of an all-reduced activation            */
+  int oneshot_tokens;  /* largest M one fused row-parallel launch handles; larger M is
+                          processed in chunks of this many tokens                      */
+  int vocab;           /* full vocabulary size for the LM-head gather (0 = unused)     */
+  int max_seqs;        /* rows of the gathered logits buffer (0 = unused)              */
+  int timeout_ms;      /* limit of every cross-GPU wait; 0 = default (5000)            */
+} b2_config;
+
+/* ---- context: replaces the NCCL process-group state the reference keeps in
+ *      nanovllm/engine/model_runner.py:26 (init) and :50-59 (exit) ------------ */
+
+/* Allocates the rank's symmetric buffers, split-K workspace, arrival counters
+ * and the host-visible status word.  Call once per process after selecting
+ * `device`. */
+int b2_ctx_create(const b2_config* cfg, b2_ctx** out);
+
+/* Writes this rank's B2_HANDLE_BYTES-byte handle; ranks exchange them with any
+ * host collective (e.g. torch.distributed.all_gather over the group that
+ * nanovllm/engine/model_runner.py:26 creates). */
+int b2_symm_export(b2_ctx* ctx, void* handle_out);
+
+/* `handles` = world * B2_HANDLE_BYTES bytes ordered by rank.  Maps every
+ * peer's buffer.  Not needed when world == 1.  A host barrier must follow
+ * before the first collective call. */
+int b2_symm_import(b2_ctx* ctx, const void* handles);
+
+/* Frees everything; call before torch.distributed.destroy_process_group
+ * (nanovllm/engine/model_runner.py:50-59), after the stream has drained. */
+int b2_ctx_destroy(b2_ctx* ctx);
+
+/* Reads the status word that bounded device-side waits write (no CUDA call, no
+ * synchronisation): *code is B2_OK or B2_ERR_TIMEOUT, *detail says which wait.
+ * Check it after the step's own synchronisation point
+ * (nanovllm/engine/model_runner.py:218, the .tolist()). */
+int b2_status(b2_ctx* ctx, int* code, int* detail);
+int b2_status_clear(b2_ctx* ctx);
+
+/* Message of the last failed CUDA call made by this library on this thread. */
+const char* b2_last_error(void);
+
+/* Number of kernels this library has launched in this process. */
+int64_t b2_launch_count(void);
+
+/* ---- GEMM: replaces F.linear in ReplicatedLinear / ColumnParallelLinear /
+ *      MergedColumnParallelLinear / QKVParallelLinear.forward
+ *      (nanovllm/layers/linear.py:51,73) and in ParallelLMHead.forward
+ *      (nanovllm/layers/embed_head.py:61) -----------------------------------
+ * C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]), bf16 in, fp32 accumulate, bf16 out.
+ * lda/ldw/ldc are row strides in elements (multiples of 8); K a multiple of 8.
+ * tcgen05 tensor-core kernel fed by TMA; the work is split along K over the
+ * SMs (stream-K) when there are fewer output tiles than SMs. */
+int b2_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias,
+            void* C, int64_t ldc, int M, int N, int K, void* stream);
+
+/* ---- row-parallel linear fused with its all-reduce, the residual add and
+ *      the next RMSNorm: replaces RowParallelLinear.forward
+ *      (nanovllm/layers/linear.py:152-156: F.linear then dist.all_reduce) AND
+ *      the RMSNorm.add_rms_forward that consumes it
+ *      (nanovllm/layers/layernorm.py:28-40; wired at
+ *      nanovllm/models/qwen3.py:155,157,182) ---------------------------------
+ * Per rank: partial = A[M,Kr] * W[N,Kr]^T (+ bias on rank 0), pushed as bf16
+ * into every peer's symmetric buffer from the GEMM epilogue; then
+ *   s = sum_over_ranks(partial) + residual_in        (fp32)
+ *   residual_out = bf16(s)
+ *   normed_out   = bf16(bf16(s * rsqrt(mean(s^2) + eps)) * norm_w)
+ * in the same launch.  residual_out may alias residual_in.  If norm_w is NULL
+ * the call is the plain RowParallelLinear.forward: normed_out receives
+ * bf16(sum) and residual_in/residual_out are ignored.  One launch per
+ * `oneshot_tokens` rows.  Every rank must issue the same sequence of
+ * collective calls (b2_rowpar_fused, b2_embed with world > 1, b2_lm_head). */
+int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias,
+                    int M, int N, int Kr, const void* residual_in, const void* norm_w, float eps,
+                    void* normed_out, void* residual_out, void* stream);
+
+/* ---- RMSNorm: replaces RMSNorm.rms_forward / add_rms_forward
+ *      (nanovllm/layers/layernorm.py:16-26, 28-40) ---------------------------
+ * x, out: [rows, dim] with row strides ldx / ldo (elements); dim % 8 == 0. */
+int b2_rmsnorm(const void* x, int64_t ldx, const void* w, float eps, int rows, int dim,
+               void* out, int64_t ldo, void* stream);
+/* out, res_out contiguous [rows, dim]; res_out may alias res; out may alias x. */
+int b2_add_rmsnorm(const void* x, const void* res, const void* w, float eps, int rows, int dim,
+                   void* out, void* res_out, void* stream);
+
+/* ---- paged-KV scatter: replaces store_kvcache / store_kvcache_kernel
+ *      (nanovllm/layers/attention.py:10-30, 33-40) ---------------------------
+ * For token i < n_tokens with slot = slot_mapping[i] (int32): if slot != -1,
+ * copy D 16-bit elements from key + i*key_stride and value + i*value_stride to
+ * k_cache + slot*D and v_cache + slot*D.  Strides in elements; D % 8 == 0 and
+ * all pointers 16-byte aligned.  Bit-exact copy. */
+int b2_store_kvcache(const void* key, int64_t key_stride, const void* value, int64_t value_stride,
+                     void* k_cache, void* v_cache, const int32_t* slot_mapping, int n_tokens, int D,
+                     void* stream);
+
+/* ---- vocab-parallel embedding: replaces VocabParallelEmbedding.forward
+ *      (nanovllm/layers/embed_head.py:34-42: mask, lookup, zero, all_reduce) --
+ * ids: int64 [M].  W: this rank's shard [vocab_end - vocab_start, H].  The
+ * rank that owns a token writes its row into every rank's buffer (the
+ * reference's sum has exactly one non-zero term per element); out[M,H] is
+ * complete on every rank when the call's kernel ends.  ctx may be NULL when
+ * the whole vocabulary is local (vocab_start = 0, world = 1). */
+int b2_embed(b2_ctx* ctx, const int64_t* ids, const void* W, int64_t vocab_start, int64_t vocab_end,
+             int M, int H, void* out, void* stream);
+
+/* ---- LM head: replaces ParallelLMHead.forward
+ *      (nanovllm/layers/embed_head.py:56-66: F.linear, dist.gather, cat) ------
+ * logits_shard[B, Vr] = h[B,H] * W[Vr,H]^T on every rank, stored straight into
+ * rank 0's [B, vocab] buffer at column rank*Vr (no separate gather or cat).
+ * On rank 0, *logits_out receives the device address of the gathered
+ * [B, vocab] bf16 buffer (owned by the context, valid until the next
+ * b2_lm_head call); other ranks get NULL, like the reference's None.
+ * row_index (int32 [B], may be NULL) selects the rows of h to use, which is
+ * the reference's h[cu_seqlens_q[1:] - 1] for prefill. */
+int b2_lm_head(b2_ctx* ctx, const void* h, int64_t ldh, const int32_t* row_index, const void* W, int64_t ldw,
+               int B, int Vr, int H, void** logits_out, void* stream);
+
+/* ---- elementwise neighbours of the path (the reference generates these with
+ *      torch.compile -> Triton) ----------------------------------------------
+ * SiluAndMul.forward (nanovllm/layers/activation.py:8-11):
+ * out[M,I] = silu(x[:, :I]) * x[:, I:], x row stride ldx. */
+int b2_silu_and_mul(const void* x, int64_t ldx, int M, int I, void* out, void* stream);
+
+/* q/k head RMSNorm (nanovllm/models/qwen3.py:82-84) + neox RoPE
+ * (nanovllm/layers/rotary_embedding.py:37-48) + paged-KV scatter of the
+ * resulting K and of V (nanovllm/layers/attention.py:59-63), in place on the
+ * qkv GEMM output [M, (nq + 2*nkv)*head_dim] (row stride ld_qkv).  positions
+ * int64 [M]; cos_sin fp32 [max_pos, head_dim] (cos || sin).  q_norm_w /
+ * k_norm_w may both be NULL (no head norm).  k_cache may be NULL (no scatter,
+ * as during the reference's warm-up, nanovllm/layers/attention.py:57,62).
+ * head_dim must be 128 or 64. */
+int b2_qk_norm_rope_store(void* qkv, int64_t ld_qkv, int M, int nq, int nkv, int head_dim,
+                          const void* q_norm_w, const void* k_norm_w, float eps,
+                          const int64_t* positions, const float* cos_sin,
+                          void* k_cache, void* v_cache, const int32_t* slot_mapping, void* stream);
+
+/* Greedy pick: out[i] = argmax_j logits[i, j] (first index on ties), int64.
+ * The reference's Sampler (nanovllm/layers/sampler.py:7-12) at temperature -> 0. */
+int b2_argmax(const void* logits, int64_t ld, int B, int V, int64_t* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200TP_H */

@@ -1,0 +1,80 @@
+"""ctypes binding of libb200tp.so (the C ABI declared in include/b200tp.h).
+
+There is no fallback: if the library has not been built, importing this module
+raises, and so does every layer that would have used it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libb200tp.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python nano-vllm_b200/build.py` (nvcc, sm_100a). "
+        "There is no CPU or PyTorch fallback for this path."
+    )
+
+lib = C.CDLL(LIB_PATH)
+
+OK, ERR_ARG, ERR_SHAPE, ERR_CUDA, ERR_STATE, ERR_TIMEOUT, ERR_UNSUPPORTED = range(7)
+HANDLE_BYTES = 64
+_ERR_NAMES = {1: "bad argument", 2: "shape outside what the context was created for", 3: "CUDA error",
+              4: "bad state (peers not imported?)", 5: "device-side wait timed out", 6: "unsupported"}
+WAIT_NAMES = {0: "none", 1: "GEMM: TMA stage never filled", 2: "GEMM: stage never freed", 3: "GEMM: accumulator never completed",
+              4: "GEMM: accumulator never drained", 5: "fused row-parallel: partial rows never arrived",
+              6: "embedding: owner row never arrived", 7: "LM head: a peer's logits never arrived"}
+
+
+class Config(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("rank", "world", "device", "max_tokens", "hidden", "oneshot_tokens", "vocab", "max_seqs", "timeout_ms")]
+
+
+class B2Error(RuntimeError):
+    pass
+
+
+_p, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
+
+SIGNATURES = {
+    "b2_ctx_create": [C.POINTER(Config), C.POINTER(_p)],
+    "b2_symm_export": [_p, _p],
+    "b2_symm_import": [_p, _p],
+    "b2_ctx_destroy": [_p],
+    "b2_status": [_p, C.POINTER(_i), C.POINTER(_i)],
+    "b2_status_clear": [_p],
+    "b2_gemm": [_p, _p, _i64, _p, _i64, _p, _p, _i64, _i, _i, _i, _p],
+    "b2_rowpar_fused": [_p, _p, _i64, _p, _i64, _p, _i, _i, _i, _p, _p, _f, _p, _p, _p],
+    "b2_rmsnorm": [_p, _i64, _p, _f, _i, _i, _p, _i64, _p],
+    "b2_add_rmsnorm": [_p, _p, _p, _f, _i, _i, _p, _p, _p],
+    "b2_store_kvcache": [_p, _i64, _p, _i64, _p, _p, _p, _i, _i, _p],
+    "b2_embed": [_p, _p, _p, _i64, _i64, _i, _i, _p, _p],
+    "b2_lm_head": [_p, _p, _i64, _p, _p, _i64, _i, _i, _i, C.POINTER(_p), _p],
+    "b2_silu_and_mul": [_p, _i64, _i, _i, _p, _p],
+    "b2_qk_norm_rope_store": [_p, _i64, _i, _i, _i, _i, _p, _p, _f, _p, _p, _p, _p, _p, _p],
+    "b2_argmax": [_p, _i64, _i, _i, _p, _p],
+}
+for _name, _args in SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.argtypes = _args
+    _fn.restype = _i
+lib.b2_last_error.restype = C.c_char_p
+lib.b2_last_error.argtypes = []
+lib.b2_launch_count.restype = _i64
+lib.b2_launch_count.argtypes = []
+
+EXPORTED = list(SIGNATURES) + ["b2_last_error", "b2_launch_count"]
+
+
+def check(rc: int, what: str) -> None:
+    if rc != OK:
+        msg = _ERR_NAMES.get(rc, f"code {rc}")
+        if rc == ERR_CUDA:
+            msg += ": " + (lib.b2_last_error() or b"").decode()
+        raise B2Error(f"{what}: {msg}")
+
+
+def launch_count() -> int:
+    return int(lib.b2_launch_count())

@@ -1,0 +1,704 @@
+// bf16 GEMM for sm_100a: TMA-fed shared-memory pipeline, tcgen05.mma with fp32
+// accumulators in tensor memory, warp-specialised (1 TMA warp, 1 MMA warp,
+// 4 epilogue warps), persistent over a stream-K partition of the work.
+//
+// D[p, q] = sum_k P[p, k] * Q[q, k]; both operands are K-major (row-major with
+// K contiguous).  P tiles have 128 rows (the MMA M dimension = 128 TMEM
+// lanes), Q tiles have BN rows (the MMA N dimension = BN TMEM columns).
+//   SWAP = false: P = activations [tokens, K], Q = weights [features, K]
+//   SWAP = true : P = weights, Q = activations (few tokens: the 128-row side
+//                 is filled by weight rows, so no tensor-core work is wasted
+//                 and every SM streams a distinct slab of the weight matrix)
+//
+// Work unit = one 64-wide K block of one output tile.  The units are dealt in
+// contiguous ranges to the CTAs; a tile whose K range is shared by several
+// CTAs is combined through fp32 partials in a workspace: the CTA that arrives
+// last at the tile's counter adds the others' partials to its own accumulator
+// and writes the output.  Nobody waits for anybody.
+//
+// EPI_PUSH: the fused row-parallel path.  The epilogue rounds the tile to bf16
+// and stores it into the inbox of every rank (its own and, over NVLink, its
+// peers'); then every CTA turns to whole rows of the inbox: it sums the
+// partials of all ranks, adds the residual, applies RMSNorm and writes the
+// results.  The inbox is data-as-flag: a slot holds the sentinel until the
+// value lands, and the reader puts the sentinel back after consuming it.
+#include <algorithm>
+
+#include "b2_common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int MAX_ROW_VECS = 6;  // 16-byte vectors of one row per thread in the reduce phase
+constexpr uint64_t PIPE_LIMIT_NS = 1000000000ull;  // no wait inside the GEMM pipeline lasts anywhere near this
+
+enum { EPI_STORE = 0, EPI_PUSH = 1 };
+
+struct GemmArgs {
+  int tilesP, tilesQ, kblocks;
+  int gemm_ctas;  // the first gemm_ctas CTAs of the grid share the GEMM units
+  int M, N;       // tokens, features of the output
+  // EPI_STORE
+  uint16_t* C;
+  int64_t ldc;
+  const uint16_t* bias;
+  // stream-K combine
+  float* ws;
+  int* counters;
+  B2Status* status;
+  // EPI_PUSH
+  unsigned char* inbox[B2_MAX_WORLD];
+  size_t parity_stride, slot_stride;
+  int world, rank;
+  const uint16_t* residual_in;
+  const uint16_t* norm_w;
+  float eps;
+  uint16_t* normed_out;
+  uint16_t* residual_out;
+  B2DeviceState* dstate;
+  uint64_t timeout_ns;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr uint32_t P_BYTES = BM * BK * 2;
+  static constexpr uint32_t Q_BYTES = BN * BK * 2;
+  static constexpr uint32_t STAGE_BYTES = P_BYTES + Q_BYTES;
+  static constexpr int STAGES = (196608 / STAGE_BYTES) > 8 ? 8 : (196608 / STAGE_BYTES);
+  static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct Partition {
+  int base, rem;
+  __host__ __device__ int u0(int c) const { return c * base + (c < rem ? c : rem); }
+  __host__ __device__ int cta_of(int u) const {
+    const int big = rem * (base + 1);
+    return u < big ? u / (base + 1) : rem + (u - big) / base;
+  }
+};
+
+struct Seg {
+  int tile, kb0, kb1;
+};
+__device__ __forceinline__ bool next_seg(int& u, int u1, int KB, Seg& s) {
+  if (u >= u1) return false;
+  s.tile = u / KB;
+  s.kb0 = u - s.tile * KB;
+  const int len = min(KB - s.kb0, u1 - u);
+  s.kb1 = s.kb0 + len;
+  u += len;
+  return true;
+}
+
+// ---------------------------------------------------------------------------
+// Output of one 32-column chunk held by a warp: thread `lane` has TMEM lane
+// (row of the P tile) q*32 + lane and columns c*32 .. c*32+31 (rows of the Q
+// tile).
+// ---------------------------------------------------------------------------
+template <bool SWAP, int EPI>
+__device__ __forceinline__ void emit_chunk(const GemmArgs& a, float (&v)[32], int p_row, int q_row0, int lane,
+                                           unsigned int parity) {
+  if (SWAP) {
+    const int feature = p_row;
+    if (a.bias != nullptr && feature < a.N) {
+      const float b = __uint_as_float(static_cast<uint32_t>(a.bias[feature]) << 16);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] += b;
+    }
+    // Lanes 2i and 2i+1 hold features f and f+1 of the same tokens.  They swap
+    // halves so that each lane stores a packed (f, f+1) pair: the even lane for
+    // even columns, the odd lane for odd columns.
+    const int fbase = feature & ~1;
+    const bool odd = lane & 1;
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      const float send = odd ? v[j] : v[j + 1];
+      const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+      const int token = q_row0 + j + (odd ? 1 : 0);
+      uint32_t w = odd ? b2::pack_bf16(recv, v[j + 1]) : b2::pack_bf16(v[j], recv);
+      if (token < a.M && fbase < a.N) {
+        if (EPI == EPI_STORE) {
+          *reinterpret_cast<uint32_t*>(a.C + token * a.ldc + fbase) = w;
+        } else {
+          w = b2::scrub_sentinel(w);
+          const size_t off = parity * a.parity_stride + a.rank * a.slot_stride +
+                             (static_cast<size_t>(token) * a.N + fbase) * 2;
+#pragma unroll
+          for (int r = 0; r < B2_MAX_WORLD; ++r)
+            if (r < a.world) *reinterpret_cast<uint32_t*>(a.inbox[r] + off) = w;
+        }
+      }
+    }
+  } else {
+    const int token = p_row;
+    if (token >= a.M) return;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int feature = q_row0 + g * 8;
+      if (feature >= a.N) break;
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = v[g * 8 + e];
+      if (a.bias != nullptr) {
+        const uint4 bv = *reinterpret_cast<const uint4*>(a.bias + feature);
+        f[0] += b2::bf16_lo(bv.x); f[1] += b2::bf16_hi(bv.x); f[2] += b2::bf16_lo(bv.y); f[3] += b2::bf16_hi(bv.y);
+        f[4] += b2::bf16_lo(bv.z); f[5] += b2::bf16_hi(bv.z); f[6] += b2::bf16_lo(bv.w); f[7] += b2::bf16_hi(bv.w);
+      }
+      uint4 w = make_uint4(b2::pack_bf16(f[0], f[1]), b2::pack_bf16(f[2], f[3]), b2::pack_bf16(f[4], f[5]),
+                           b2::pack_bf16(f[6], f[7]));
+      if (EPI == EPI_STORE) {
+        *reinterpret_cast<uint4*>(a.C + token * a.ldc + feature) = w;
+      } else {
+        w.x = b2::scrub_sentinel(w.x); w.y = b2::scrub_sentinel(w.y);
+        w.z = b2::scrub_sentinel(w.z); w.w = b2::scrub_sentinel(w.w);
+        const size_t off = parity * a.parity_stride + a.rank * a.slot_stride +
+                           (static_cast<size_t>(token) * a.N + feature) * 2;
+#pragma unroll
+        for (int r = 0; r < B2_MAX_WORLD; ++r)
+          if (r < a.world) *reinterpret_cast<uint4*>(a.inbox[r] + off) = w;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Reduce phase of the fused row-parallel call: one CTA per token row.
+// S = number of source ranks.
+// ---------------------------------------------------------------------------
+template <int S>
+__device__ __forceinline__ void reduce_rows(const GemmArgs& a, unsigned int parity, float* red, volatile int* gave_up) {
+  const int nvec = a.N >> 3;
+  const int tid = threadIdx.x;
+  unsigned char* my = a.inbox[a.rank] + parity * a.parity_stride;
+  const uint4 sentinel = make_uint4(B2_SENTINEL32, B2_SENTINEL32, B2_SENTINEL32, B2_SENTINEL32);
+  for (int row = blockIdx.x; row < a.M; row += gridDim.x) {
+    float acc[MAX_ROW_VECS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < MAX_ROW_VECS; ++it) {
+      const int v = tid + it * NUM_THREADS;
+      if (v < nvec) {
+        const size_t off = (static_cast<size_t>(row) * a.N + v * 8) * 2;
+        uint4 val[S];
+        bool pending = true;
+        uint64_t t0 = 0;
+        for (uint32_t spin = 0; pending; ++spin) {
+          pending = false;
+#pragma unroll
+          for (int s = 0; s < S; ++s) val[s] = b2::ld_volatile_v4(my + s * a.slot_stride + off);
+#pragma unroll
+          for (int s = 0; s < S; ++s) pending |= b2::has_sentinel(val[s]);
+          if (pending && (spin & 0x3F) == 0x3F) {
+            // one expired wait ends every later wait of this CTA at once
+            if (*gave_up) break;
+            const uint64_t now = b2::globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > a.timeout_ns) {
+              *gave_up = 1;
+              b2::report_timeout(a.status, B2_WAIT_PARTIALS);
+              break;
+            }
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[it][e] = 0.f;
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+          acc[it][0] += b2::bf16_lo(val[s].x); acc[it][1] += b2::bf16_hi(val[s].x);
+          acc[it][2] += b2::bf16_lo(val[s].y); acc[it][3] += b2::bf16_hi(val[s].y);
+          acc[it][4] += b2::bf16_lo(val[s].z); acc[it][5] += b2::bf16_hi(val[s].z);
+          acc[it][6] += b2::bf16_lo(val[s].w); acc[it][7] += b2::bf16_hi(val[s].w);
+          *reinterpret_cast<uint4*>(my + s * a.slot_stride + off) = sentinel;  // consumed
+        }
+        const size_t eoff = static_cast<size_t>(row) * a.N + v * 8;
+        if (a.norm_w != nullptr) {
+          const uint4 rv = *reinterpret_cast<const uint4*>(a.residual_in + eoff);
+          acc[it][0] += b2::bf16_lo(rv.x); acc[it][1] += b2::bf16_hi(rv.x);
+          acc[it][2] += b2::bf16_lo(rv.y); acc[it][3] += b2::bf16_hi(rv.y);
+          acc[it][4] += b2::bf16_lo(rv.z); acc[it][5] += b2::bf16_hi(rv.z);
+          acc[it][6] += b2::bf16_lo(rv.w); acc[it][7] += b2::bf16_hi(rv.w);
+          *reinterpret_cast<uint4*>(a.residual_out + eoff) =
+              make_uint4(b2::pack_bf16(acc[it][0], acc[it][1]), b2::pack_bf16(acc[it][2], acc[it][3]),
+                         b2::pack_bf16(acc[it][4], acc[it][5]), b2::pack_bf16(acc[it][6], acc[it][7]));
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ss += acc[it][e] * acc[it][e];
+        } else {
+          *reinterpret_cast<uint4*>(a.normed_out + eoff) =
+              make_uint4(b2::pack_bf16(acc[it][0], acc[it][1]), b2::pack_bf16(acc[it][2], acc[it][3]),
+                         b2::pack_bf16(acc[it][4], acc[it][5]), b2::pack_bf16(acc[it][6], acc[it][7]));
+        }
+      }
+    }
+    if (a.norm_w == nullptr) continue;  // plain all-reduce: done with this row (uniform across the CTA)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    __syncthreads();  // red[] free again
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NUM_THREADS / 32; ++i) tot += red[i];
+    const float rstd = rsqrtf(tot / static_cast<float>(a.N) + a.eps);
+#pragma unroll
+    for (int it = 0; it < MAX_ROW_VECS; ++it) {
+      const int v = tid + it * NUM_THREADS;
+      if (v < nvec) {
+        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(a.norm_w + v * 8));
+        float o[8];
+        o[0] = b2::bf16_round(acc[it][0] * rstd) * b2::bf16_lo(wv.x); o[1] = b2::bf16_round(acc[it][1] * rstd) * b2::bf16_hi(wv.x);
+        o[2] = b2::bf16_round(acc[it][2] * rstd) * b2::bf16_lo(wv.y); o[3] = b2::bf16_round(acc[it][3] * rstd) * b2::bf16_hi(wv.y);
+        o[4] = b2::bf16_round(acc[it][4] * rstd) * b2::bf16_lo(wv.z); o[5] = b2::bf16_round(acc[it][5] * rstd) * b2::bf16_hi(wv.z);
+        o[6] = b2::bf16_round(acc[it][6] * rstd) * b2::bf16_lo(wv.w); o[7] = b2::bf16_round(acc[it][7] * rstd) * b2::bf16_hi(wv.w);
+        *reinterpret_cast<uint4*>(a.normed_out + static_cast<size_t>(row) * a.N + v * 8) =
+            make_uint4(b2::pack_bf16(o[0], o[1]), b2::pack_bf16(o[2], o[3]), b2::pack_bf16(o[4], o[5]), b2::pack_bf16(o[6], o[7]));
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------
+template <int BN, bool SWAP, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const GemmArgs a) {
+  using C = Cfg<BN>;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw_addr = b2::smem_u32(smem_raw);
+  unsigned char* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  const uint32_t smem_base = b2::smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES);
+  const uint32_t bar_full = b2::smem_u32(bars);
+  const uint32_t bar_empty = bar_full + STAGES * 8;
+  const uint32_t bar_tfull = bar_empty + STAGES * 8;
+  const uint32_t bar_tempty = bar_tfull + 2 * 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile unsigned int* seq_slot = reinterpret_cast<volatile unsigned int*>(tmem_slot + 2);
+  __shared__ float red[NUM_THREADS / 32];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x;
+  const int KB = a.kblocks;
+  const int tiles = a.tilesP * a.tilesQ;
+  const int U = tiles * KB;
+  const bool has_gemm = cta < a.gemm_ctas;
+  Partition part;
+  part.base = U / a.gemm_ctas;
+  part.rem = U % a.gemm_ctas;
+  const int u_begin = has_gemm ? part.u0(cta) : 0;
+  const int u_end = has_gemm ? part.u0(cta + 1) : 0;
+
+  if (threadIdx.x == 0) {
+    b2::tma_prefetch_desc(&tmP);
+    b2::tma_prefetch_desc(&tmQ);
+    for (int s = 0; s < STAGES; ++s) {
+      b2::mbar_init(bar_full + s * 8, 1);
+      b2::mbar_init(bar_empty + s * 8, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      b2::mbar_init(bar_tfull + i * 8, 1);
+      b2::mbar_init(bar_tempty + i * 8, 4);
+    }
+    *abort_flag = 0;
+    if (EPI == EPI_PUSH) *seq_slot = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq);
+    b2::mbar_fence_init();
+  }
+  if (warp == 1 && has_gemm) {
+    b2::tmem_alloc(b2::smem_u32(tmem_slot), C::TMEM_COLS);
+    b2::tmem_relinquish();
+  }
+  b2::tc_fence_before();
+  __syncthreads();
+  b2::tc_fence_after();
+  const uint32_t tmem_base = has_gemm ? *tmem_slot : 0;
+  const unsigned int parity = (EPI == EPI_PUSH) ? (*seq_slot & 1u) : 0u;
+
+  if (has_gemm) {
+    if (warp == 0) {
+      // ---------------- TMA producer ----------------
+      if (lane == 0) {
+        const uint64_t polP = SWAP ? b2::kEvictFirst : b2::kEvictNormal;
+        const uint64_t polQ = SWAP ? b2::kEvictLast : b2::kEvictNormal;
+        int stage = 0;
+        uint32_t phase = 0;
+        int u = u_begin;
+        Seg s;
+        bool ok = true;
+        while (ok && next_seg(u, u_end, KB, s)) {
+          const int tp = s.tile / a.tilesQ, tq = s.tile - tp * a.tilesQ;
+          for (int kb = s.kb0; kb < s.kb1; ++kb) {
+            if (!b2::mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_SMEM_EMPTY)) { ok = false; break; }
+            const uint32_t fb = bar_full + stage * 8;
+            b2::mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
+            const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
+            b2::tma_load_2d(dst, &tmP, fb, kb * BK, tp * BM, polP);
+            b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, kb * BK, tq * BN, polQ);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // ---------------- MMA issuer ----------------
+      if (lane == 0) {
+        constexpr uint32_t idesc = b2::umma_idesc_bf16(BN);
+        int stage = 0;
+        uint32_t phase = 0;
+        int u = u_begin, seg = 0;
+        Seg s;
+        bool ok = true;
+        while (ok && next_seg(u, u_end, KB, s)) {
+          const int acc = seg & 1;
+          const uint32_t use = static_cast<uint32_t>(seg >> 1);  // how often this accumulator was used before
+          if (!b2::mbar_wait(bar_tempty + acc * 8, (use & 1) ^ 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_TMEM_EMPTY)) break;
+          b2::tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * BN;
+          for (int kb = s.kb0; kb < s.kb1; ++kb) {
+            if (!b2::mbar_wait(bar_full + stage * 8, phase, abort_flag, PIPE_LIMIT_NS, B2_WAIT_SMEM_FULL)) { ok = false; break; }
+            b2::tc_fence_after();
+            const uint32_t sp = smem_base + stage * C::STAGE_BYTES;
+            const uint64_t dp = b2::umma_smem_desc(sp);
+            const uint64_t dq = b2::umma_smem_desc(sp + C::P_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              // advancing K by 16 elements = 32 bytes inside the 128-byte swizzle row
+              b2::umma_bf16(d_tmem, dp + 2 * k, dq + 2 * k, idesc, (kb > s.kb0 || k > 0) ? 1u : 0u);
+            }
+            b2::umma_commit(bar_empty + stage * 8);  // stage reusable once these MMAs have read it
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (!ok) break;
+          b2::umma_commit(bar_tfull + acc * 8);
+          ++seg;
+        }
+      }
+    } else {
+      // ---------------- epilogue warps ----------------
+      const int q = warp & 3;  // TMEM lane quadrant this warp may read
+      int u = u_begin, seg = 0;
+      Seg s;
+      while (next_seg(u, u_end, KB, s)) {
+        const int acc = seg & 1;
+        const uint32_t use = static_cast<uint32_t>(seg >> 1);
+        if (!b2::mbar_wait(bar_tfull + acc * 8, use & 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_TMEM_FULL)) break;
+        b2::tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+        const int tp = s.tile / a.tilesQ, tq = s.tile - tp * a.tilesQ;
+        const int p_row = tp * BM + q * 32 + lane;
+        const bool whole = (s.kb0 == 0 && s.kb1 == KB);
+        if (whole) {
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            b2::tmem_ld_32x32(taddr + c * 32, r);
+            b2::tc_wait_ld();
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            emit_chunk<SWAP, EPI>(a, v, p_row, tq * BN + c * 32, lane, parity);
+          }
+        } else {
+          // this CTA holds only part of the tile's K range
+          const int my_slot = (seg == 0) ? 0 : 1;
+          float* mine = a.ws + ((static_cast<size_t>(cta) * 2 + my_slot) * 4 + q) * (BN * 32);
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            b2::tmem_ld_32x32(taddr + c * 32, r);
+            b2::tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) mine[(c * 32 + j) * 32 + lane] = __uint_as_float(r[j]);
+          }
+          __threadfence();
+          __syncwarp();
+          const int c_first = part.cta_of(s.tile * KB), c_last = part.cta_of(s.tile * KB + KB - 1);
+          int old = 0;
+          if (lane == 0) old = atomicAdd(a.counters + s.tile * 4 + q, 1);
+          old = __shfl_sync(0xffffffffu, old, 0);
+          if (old == c_last - c_first) {
+            // last to arrive: every other contributor's partial is complete
+            __threadfence();
+            if (lane == 0) a.counters[s.tile * 4 + q] = 0;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+              uint32_t r[32];
+              b2::tmem_ld_32x32(taddr + c * 32, r);
+              b2::tc_wait_ld();
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+              for (int cc = c_first; cc <= c_last; ++cc) {
+                if (cc == cta) continue;
+                const int slot = (part.u0(cc) / KB == s.tile) ? 0 : 1;
+                const float* other = a.ws + ((static_cast<size_t>(cc) * 2 + slot) * 4 + q) * (BN * 32) + c * 32 * 32 + lane;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += b2::ld_cg_f32(other + j * 32);
+              }
+              emit_chunk<SWAP, EPI>(a, v, p_row, tq * BN + c * 32, lane, parity);
+            }
+          }
+        }
+        b2::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) b2::mbar_arrive(bar_tempty + acc * 8);
+        ++seg;
+      }
+    }
+  }
+
+  // ---- all roles meet; tensor memory goes back ------------------------------
+  __syncwarp();
+  b2::tc_fence_before();
+  __syncthreads();
+  b2::tc_fence_after();
+  const int aborted = *abort_flag;
+  if (aborted) {
+    // let bulk copies that may still be in flight land before the CTA leaves
+    for (int i = 0; i < 100; ++i) __nanosleep(2000);
+    if (threadIdx.x == 0) b2::report_timeout(a.status, aborted);
+  }
+  if (warp == 1 && has_gemm) b2::tmem_dealloc(tmem_base, C::TMEM_COLS);
+
+  if (EPI == EPI_PUSH) {
+    if (!aborted) {
+      switch (a.world) {
+        case 1: reduce_rows<1>(a, parity, red, abort_flag); break;
+        case 2: reduce_rows<2>(a, parity, red, abort_flag); break;
+        case 4: reduce_rows<4>(a, parity, red, abort_flag); break;
+        default: reduce_rows<8>(a, parity, red, abort_flag); break;
+      }
+    }
+    // the last CTA to finish advances the launch parity for the next call
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const unsigned int prev = atomicAdd(&a.dstate->rowpar_done, 1u);
+      if (prev == gridDim.x - 1) {
+        a.dstate->rowpar_done = 0;
+        a.dstate->rowpar_seq += 1;
+        __threadfence();
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <int BN, bool SWAP, int EPI>
+int launch_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmArgs& args, int grid, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    B2_CUDA(cudaFuncSetAttribute(gemm_kernel<BN, SWAP, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
+    configured = true;
+  }
+  gemm_kernel<BN, SWAP, EPI><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(tmP, tmQ, args);
+  b2::count_launch();
+  B2_CUDA(cudaGetLastError());
+  return B2_OK;
+}
+
+template <int EPI>
+int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K, GemmArgs& args,
+                int min_grid, cudaStream_t stream) {
+  const bool swap = M <= 256;
+  int bn;
+  if (swap) bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  else bn = (N >= 256) ? 256 : (N > 64 ? 128 : 64);
+  const int rowsP = swap ? N : M, rowsQ = swap ? M : N;
+  args.tilesP = (rowsP + BM - 1) / BM;
+  args.tilesQ = (rowsQ + bn - 1) / bn;
+  args.kblocks = (K + BK - 1) / BK;
+  args.M = M;
+  args.N = N;
+  args.ws = ctx->splitk_ws;
+  args.counters = ctx->tile_counters;
+  args.status = ctx->status_dev;
+  const int64_t tiles = static_cast<int64_t>(args.tilesP) * args.tilesQ;
+  if (tiles > ctx->tile_counter_cap) return B2_ERR_SHAPE;
+  const int64_t U = tiles * args.kblocks;
+  if (U > (1ll << 30)) return B2_ERR_SHAPE;
+  // every CTA should stream at least ~8 K blocks, or splitting costs more than it saves
+  int64_t g = std::max<int64_t>(1, U / 8);
+  g = std::min<int64_t>(g, ctx->num_sms);
+  g = std::min<int64_t>(g, U);
+  args.gemm_ctas = static_cast<int>(g);
+  const int grid = std::max(args.gemm_ctas, std::min(min_grid, ctx->num_sms));
+
+  CUtensorMap tmP, tmQ;
+  const void* pP = swap ? W : A;
+  const void* pQ = swap ? A : W;
+  const int64_t ldP = swap ? ldw : lda, ldQ = swap ? lda : ldw;
+  int rc = b2::encode_tmap_2d(&tmP, pP, K, rowsP, ldP, BK, BM);
+  if (rc != B2_OK) return rc;
+  rc = b2::encode_tmap_2d(&tmQ, pQ, K, rowsQ, ldQ, BK, bn);
+  if (rc != B2_OK) return rc;
+
+  if (swap) {
+    switch (bn) {
+      case 32: return launch_inst<32, true, EPI>(tmP, tmQ, args, grid, stream);
+      case 64: return launch_inst<64, true, EPI>(tmP, tmQ, args, grid, stream);
+      case 128: return launch_inst<128, true, EPI>(tmP, tmQ, args, grid, stream);
+      default: return launch_inst<256, true, EPI>(tmP, tmQ, args, grid, stream);
+    }
+  }
+  switch (bn) {
+    case 64: return launch_inst<64, false, EPI>(tmP, tmQ, args, grid, stream);
+    case 128: return launch_inst<128, false, EPI>(tmP, tmQ, args, grid, stream);
+    default: return launch_inst<256, false, EPI>(tmP, tmQ, args, grid, stream);
+  }
+}
+
+int check_operands(const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K) {
+  if (M < 0 || N <= 0 || K <= 0) return B2_ERR_ARG;
+  if (!A || !W || !aligned16(A) || !aligned16(W)) return B2_ERR_ARG;
+  if (K % 8 != 0 || N % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || lda < K || ldw < K) return B2_ERR_ARG;
+  return B2_OK;
+}
+
+// rows of h picked by index into a contiguous staging buffer (the prefill
+// "last token of every sequence" selection)
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint16_t* __restrict__ h, int64_t ldh,
+                                                          const int32_t* __restrict__ idx, int B, int H,
+                                                          uint16_t* __restrict__ out) {
+  const int vpr = H >> 3;
+  const int64_t total = static_cast<int64_t>(B) * vpr;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int b = static_cast<int>(i / vpr), v = static_cast<int>(i - static_cast<int64_t>(b) * vpr);
+    *reinterpret_cast<uint4*>(out + static_cast<int64_t>(b) * H + v * 8) =
+        __ldg(reinterpret_cast<const uint4*>(h + idx[b] * ldh + v * 8));
+  }
+}
+
+// Completion of the logits gather.  It runs after the GEMM that stored this
+// rank's slice into rank 0's buffer (stream order makes those stores visible
+// before anything this kernel writes).  Ranks other than 0 publish the call
+// number in rank 0's flag word; rank 0 waits until every peer has published it.
+__global__ void lm_head_sync_kernel(int rank, int world, unsigned int* flags_rank0, B2DeviceState* dstate, B2Status* status,
+                                    uint64_t timeout_ns) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const unsigned int want = dstate->lmhead_seq + 1;
+  if (rank != 0) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags_rank0 + rank), "r"(want) : "memory");
+  } else {
+    const uint64_t t0 = b2::globaltimer_ns();
+    for (int r = 1; r < world; ++r) {
+      for (uint32_t spin = 0;; ++spin) {
+        unsigned int got;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(flags_rank0 + r) : "memory");
+        if (static_cast<int>(got - want) >= 0) break;
+        if ((spin & 0xFF) == 0xFF && b2::globaltimer_ns() - t0 > timeout_ns) {
+          b2::report_timeout(status, B2_WAIT_LOGITS);
+          break;
+        }
+      }
+    }
+  }
+  dstate->lmhead_seq = want;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b2_lm_head(b2_ctx* ctx, const void* h, int64_t ldh, const int32_t* row_index, const void* W, int64_t ldw, int B, int Vr, int H,
+               void** logits_out, void* stream) {
+  if (ctx == nullptr || logits_out == nullptr) return B2_ERR_ARG;
+  *logits_out = nullptr;
+  int rc = check_operands(h, ldh, W, ldw, B, Vr, H);
+  if (rc != B2_OK) return rc;
+  const int world = ctx->cfg.world, rank = ctx->cfg.rank;
+  if (ctx->cfg.vocab <= 0 || ctx->cfg.max_seqs <= 0) return B2_ERR_STATE;
+  if (B > ctx->cfg.max_seqs || static_cast<int64_t>(Vr) * world != ctx->cfg.vocab || H > ctx->cfg.hidden) return B2_ERR_SHAPE;
+  if (!ctx->peers_ready) return B2_ERR_STATE;
+  if (B == 0) return B2_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const void* A = h;
+  int64_t lda = ldh;
+  if (row_index != nullptr) {
+    const int64_t work = static_cast<int64_t>(B) * (H / 8);
+    const int grid = static_cast<int>(std::min<int64_t>((work + 255) / 256, ctx->num_sms * 4));
+    gather_rows_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(h), ldh, row_index, B, H,
+                                            reinterpret_cast<uint16_t*>(ctx->gather_rows));
+    b2::count_launch();
+    B2_CUDA(cudaGetLastError());
+    A = ctx->gather_rows;
+    lda = H;
+  }
+  GemmArgs args{};
+  args.C = reinterpret_cast<uint16_t*>(ctx->peer[0] + ctx->off_logits) + static_cast<size_t>(rank) * Vr;
+  args.ldc = ctx->cfg.vocab;
+  rc = launch_gemm<EPI_STORE>(ctx, A, lda, W, ldw, B, Vr, H, args, 0, s);
+  if (rc != B2_OK) return rc;
+  if (world > 1) {
+    lm_head_sync_kernel<<<1, 32, 0, s>>>(rank, world, reinterpret_cast<unsigned int*>(ctx->peer[0] + ctx->off_flags), ctx->dstate,
+                                         ctx->status_dev, static_cast<uint64_t>(ctx->cfg.timeout_ms) * 1000000ull);
+    b2::count_launch();
+    B2_CUDA(cudaGetLastError());
+  }
+  if (rank == 0) *logits_out = ctx->symm + ctx->off_logits;
+  return B2_OK;
+}
+
+int b2_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias, void* C, int64_t ldc, int M,
+            int N, int K, void* stream) {
+  if (ctx == nullptr) return B2_ERR_ARG;
+  int rc = check_operands(A, lda, W, ldw, M, N, K);
+  if (rc != B2_OK) return rc;
+  if (M == 0) return B2_OK;
+  if (!C || !aligned16(C) || ldc % 8 != 0 || ldc < N) return B2_ERR_ARG;
+  if (bias != nullptr && !aligned16(bias)) return B2_ERR_ARG;
+  GemmArgs args{};
+  args.C = static_cast<uint16_t*>(C);
+  args.ldc = ldc;
+  args.bias = static_cast<const uint16_t*>(bias);
+  return launch_gemm<EPI_STORE>(ctx, A, lda, W, ldw, M, N, K, args, 0, static_cast<cudaStream_t>(stream));
+}
+
+int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias, int M, int N, int Kr,
+                    const void* residual_in, const void* norm_w, float eps, void* normed_out, void* residual_out, void* stream) {
+  if (ctx == nullptr) return B2_ERR_ARG;
+  int rc = check_operands(A, lda, W, ldw, M, N, Kr);
+  if (rc != B2_OK) return rc;
+  if (M == 0) return B2_OK;
+  if (!ctx->peers_ready) return B2_ERR_STATE;
+  if (N > ctx->cfg.hidden || N > MAX_ROW_VECS * NUM_THREADS * 8) return B2_ERR_SHAPE;
+  if (!normed_out || !aligned16(normed_out)) return B2_ERR_ARG;
+  if (norm_w != nullptr && (!residual_in || !residual_out || !aligned16(residual_in) || !aligned16(residual_out) || !aligned16(norm_w)))
+    return B2_ERR_ARG;
+  if (bias != nullptr && !aligned16(bias)) return B2_ERR_ARG;
+  const int chunk = ctx->cfg.oneshot_tokens;
+  for (int m0 = 0; m0 < M; m0 += chunk) {
+    const int m = std::min(chunk, M - m0);
+    GemmArgs args{};
+    args.bias = (ctx->cfg.rank == 0) ? static_cast<const uint16_t*>(bias) : nullptr;  // bias enters the sum once
+    for (int r = 0; r < ctx->cfg.world; ++r) args.inbox[r] = ctx->peer[r] + ctx->off_rowpar;
+    args.slot_stride = static_cast<size_t>(ctx->cfg.oneshot_tokens) * ctx->cfg.hidden * 2;
+    args.parity_stride = args.slot_stride * ctx->cfg.world;
+    args.world = ctx->cfg.world;
+    args.rank = ctx->cfg.rank;
+    const size_t eoff = static_cast<size_t>(m0) * N;
+    args.residual_in = residual_in ? static_cast<const uint16_t*>(residual_in) + eoff : nullptr;
+    args.norm_w = static_cast<const uint16_t*>(norm_w);
+    args.eps = eps;
+    args.normed_out = static_cast<uint16_t*>(normed_out) + eoff;
+    args.residual_out = residual_out ? static_cast<uint16_t*>(residual_out) + eoff : nullptr;
+    args.dstate = ctx->dstate;
+    args.timeout_ns = static_cast<uint64_t>(ctx->cfg.timeout_ms) * 1000000ull;
+    rc = launch_gemm<EPI_PUSH>(ctx, static_cast<const uint16_t*>(A) + static_cast<size_t>(m0) * lda, lda, W, ldw, m, N, Kr, args, m,
+                               static_cast<cudaStream_t>(stream));
+    if (rc != B2_OK) return rc;
+  }
+  return B2_OK;
+}
+
+}  // extern "C"

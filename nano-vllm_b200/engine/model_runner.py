@@ -1,0 +1,257 @@
+"""The part of the model runner that hosts the tensor-parallel layer path.
+
+It covers what nanovllm/engine/model_runner.py does around the model on each
+rank: runtime set-up between device selection and model construction (:26-31),
+KV-cache allocation and binding (:103-121), batch -> tensors for prefill and
+decode (:123-188), CUDA-graph capture and replay for decode (:195-212,
+:222-257) and teardown order (:50-59).  The scheduler, block manager,
+tokenizer and the shared-memory RPC between ranks stay outside: callers hand
+in token lists and block tables (every rank must be given the same batch).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from ..layers.sampler import Sampler
+from ..models.qwen3 import Qwen3ForCausalLM
+from ..runtime import get_runtime, init_runtime, shutdown_runtime
+from ..utils.context import reset_context, set_context
+
+
+@dataclass
+class ModelConfig:
+    """The fields of a HF Qwen3 config the model reads (nanovllm/models/qwen3.py:127-143,167-171,199-203)."""
+    hidden_size: int
+    num_attention_heads: int
+    num_key_value_heads: int
+    head_dim: int
+    intermediate_size: int
+    num_hidden_layers: int
+    vocab_size: int
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    max_position_embeddings: int = 40960
+    tie_word_embeddings: bool = False
+    attention_bias: bool = False
+    hidden_act: str = "silu"
+    rope_scaling: dict | None = None
+
+
+QWEN3_0_6B = dict(hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072,
+                  num_hidden_layers=28, vocab_size=151936, tie_word_embeddings=True)
+QWEN3_8B = dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+                num_hidden_layers=36, vocab_size=151936, tie_word_embeddings=False)
+QWEN3_32B = dict(hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, head_dim=128, intermediate_size=25600,
+                 num_hidden_layers=64, vocab_size=151936, tie_word_embeddings=False)
+
+
+@dataclass
+class Seq:
+    """Minimal per-request state: the token ids so far, the KV blocks they
+    occupy and how many leading tokens are already in the cache."""
+    token_ids: list[int]
+    block_table: list[int] = field(default_factory=list)
+    num_cached_tokens: int = 0
+
+    def __len__(self):
+        return len(self.token_ids)
+
+
+def random_init_(model: torch.nn.Module, seed: int, tp_rank: int) -> None:
+    """Seeded N(0, 0.02) weights generated on the device (norm weights stay 1).
+    Each rank draws its own shard: enough for throughput runs, where only the
+    shapes matter; parity tests load shards of one full model instead."""
+    g = torch.Generator(device="cuda").manual_seed(seed * 1000 + tp_rank)
+    for name, p in model.named_parameters():
+        if "norm" in name:
+            p.data.fill_(1.0)
+        else:
+            p.data.copy_(torch.empty(p.shape, dtype=torch.float32, device=p.device).normal_(0, 0.02, generator=g))
+
+
+class ModelRunner:
+
+    def __init__(self, config: ModelConfig, *, max_num_seqs: int = 512, max_model_len: int = 4096, max_num_batched_tokens: int = 16384,
+                 kvcache_block_size: int = 256, num_kvcache_blocks: int | None = None, gpu_memory_utilization: float = 0.9,
+                 enforce_eager: bool = False, oneshot_tokens: int = 1024, timeout_ms: int = 5000, seed: int = 0,
+                 full_weights: dict | None = None):
+        assert dist.is_initialized(), "create the process group first (world size 1 included), as the reference does"
+        self.config = config
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.block_size = kvcache_block_size
+        self.max_num_seqs, self.max_model_len, self.max_num_batched_tokens = max_num_seqs, max_model_len, max_num_batched_tokens
+        self.enforce_eager = enforce_eager
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        # symmetric buffers exist before the layers are built, so graph capture sees fixed addresses
+        self.runtime = init_runtime(max_tokens=max_num_batched_tokens, hidden=config.hidden_size, oneshot_tokens=oneshot_tokens,
+                                    vocab=config.vocab_size, max_seqs=max_num_seqs, timeout_ms=timeout_ms)
+        prev_dtype = torch.get_default_dtype()
+        torch.set_default_dtype(torch.bfloat16)
+        torch.set_default_device(self.device)
+        try:
+            self.model = Qwen3ForCausalLM(config)
+            if full_weights is not None:
+                self.model.load_full_weights(full_weights)
+            else:
+                random_init_(self.model, seed, self.rank)
+            self.sampler = Sampler()
+            self._allocate_kv_cache(num_kvcache_blocks, gpu_memory_utilization)
+            self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+            if not enforce_eager:
+                self._capture_graphs()
+        finally:
+            torch.set_default_device("cpu")
+            torch.set_default_dtype(prev_dtype)
+
+    # ---- teardown (reference :50-59) --------------------------------------
+    def exit(self):
+        self.graphs = {}
+        self.graph_pool = None
+        torch.cuda.synchronize()
+        shutdown_runtime()
+
+    # ---- KV cache (reference :103-121) -------------------------------------
+    def _allocate_kv_cache(self, num_blocks: int | None, utilization: float):
+        c = self.config
+        self.num_kv_heads = c.num_key_value_heads // self.world
+        block_bytes = 2 * c.num_hidden_layers * self.block_size * self.num_kv_heads * c.head_dim * 2
+        if num_blocks is None:
+            free, total = torch.cuda.mem_get_info()
+            budget = int(total * utilization) - (total - free)
+            # activations of the largest prefill step: a few [tokens, widest layer output] bf16 tensors
+            widest = max(2 * c.intermediate_size // self.world, c.hidden_size, (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim // self.world)
+            budget -= 6 * self.max_num_batched_tokens * widest * 2
+            num_blocks = budget // block_bytes
+        assert num_blocks > 0, "no memory left for the KV cache"
+        self.num_kvcache_blocks = int(num_blocks)
+        self.kv_cache = torch.zeros(2, c.num_hidden_layers, self.num_kvcache_blocks, self.block_size, self.num_kv_heads, c.head_dim,
+                                    dtype=torch.bfloat16, device=self.device)
+        for i, layer in enumerate(self.model.model.layers):
+            layer.self_attn.attn.k_cache = self.kv_cache[0, i]
+            layer.self_attn.attn.v_cache = self.kv_cache[1, i]
+
+    # ---- batch -> tensors -----------------------------------------------------
+    def _h2d(self, values, dtype):
+        return torch.tensor(values, dtype=dtype, pin_memory=True).to(self.device, non_blocking=True)
+
+    def _block_tables(self, seqs: list[Seq]):
+        width = max(len(s.block_table) for s in seqs)
+        return self._h2d([s.block_table + [-1] * (width - len(s.block_table)) for s in seqs], torch.int32)
+
+    def prepare_prefill(self, seqs: list[Seq], num_new: list[int] | None = None):
+        """Tokens [num_cached, num_cached + new) of each sequence are computed;
+        their K/V go to the slots their block table assigns (reference :129-170)."""
+        ids, pos, slots, cu_q, cu_k = [], [], [], [0], [0]
+        max_q = max_k = 0
+        bs = self.block_size
+        for i, s in enumerate(seqs):
+            start = s.num_cached_tokens
+            end = len(s) if num_new is None else start + num_new[i]
+            ids.extend(s.token_ids[start:end])
+            pos.extend(range(start, end))
+            cu_q.append(cu_q[-1] + end - start)
+            cu_k.append(cu_k[-1] + end)
+            max_q, max_k = max(max_q, end - start), max(max_k, end)
+            if s.block_table:
+                slots.extend(s.block_table[p // bs] * bs + p % bs for p in range(start, end))
+        block_tables = self._block_tables(seqs) if cu_k[-1] > cu_q[-1] else None
+        ids_t, pos_t = self._h2d(ids, torch.int64), self._h2d(pos, torch.int64)
+        set_context(True, self._h2d(cu_q, torch.int32), self._h2d(cu_k, torch.int32), max_q, max_k,
+                    self._h2d(slots, torch.int32) if slots else None, None, block_tables)
+        return ids_t, pos_t
+
+    def prepare_decode(self, seqs: list[Seq]):
+        """One new token per sequence: the last one of its list (reference :172-188)."""
+        bs = self.block_size
+        ids = [s.token_ids[-1] for s in seqs]
+        pos = [len(s) - 1 for s in seqs]
+        slots = [s.block_table[(len(s) - 1) // bs] * bs + (len(s) - 1) % bs for s in seqs]
+        lens = [len(s) for s in seqs]
+        set_context(False, slot_mapping=self._h2d(slots, torch.int32), context_lens=self._h2d(lens, torch.int32),
+                    block_tables=self._block_tables(seqs))
+        return self._h2d(ids, torch.int64), self._h2d(pos, torch.int64)
+
+    # ---- forward ---------------------------------------------------------------
+    @torch.inference_mode()
+    def run_model(self, input_ids: torch.Tensor, positions: torch.Tensor, is_prefill: bool):
+        from ..utils.context import get_context
+        n = input_ids.size(0)
+        if is_prefill or self.enforce_eager or n > self.graph_bs[-1]:
+            return self.model.compute_logits(self.model(input_ids, positions))
+        ctx = get_context()
+        bs = next(b for b in self.graph_bs if b >= n)
+        gv = self.graph_vars
+        gv["input_ids"][:n] = input_ids
+        gv["positions"][:n] = positions
+        gv["slot_mapping"].fill_(-1)  # padded rows store nothing
+        gv["slot_mapping"][:n] = ctx.slot_mapping
+        gv["context_lens"].zero_()
+        gv["context_lens"][:n] = ctx.context_lens
+        gv["block_tables"][:n, :ctx.block_tables.size(1)] = ctx.block_tables
+        self.graphs[bs].replay()
+        return self.model.compute_logits(gv["outputs"][:n])
+
+    @torch.inference_mode()
+    def step(self, seqs: list[Seq], is_prefill: bool, temperatures: list[float] | None = None, num_new: list[int] | None = None):
+        """One forward pass + sampling.  Returns the new token ids on rank 0
+        (None elsewhere).  temperatures=None means greedy (argmax)."""
+        ids, pos = self.prepare_prefill(seqs, num_new) if is_prefill else self.prepare_decode(seqs)
+        logits = self.run_model(ids, pos, is_prefill)
+        tokens = None
+        if self.rank == 0:
+            if temperatures is None:
+                tokens = Sampler.greedy(logits).tolist()
+            else:
+                tokens = self.sampler(logits, self._h2d(temperatures, torch.float32)).tolist()
+        else:
+            torch.cuda.current_stream().synchronize()
+        reset_context()
+        self.runtime.check_status()
+        return tokens
+
+    # ---- CUDA graphs (reference :222-257) -----------------------------------------
+    @torch.inference_mode()
+    def _capture_graphs(self):
+        c = self.config
+        max_bs = min(self.max_num_seqs, 512)
+        max_blocks = (self.max_model_len + self.block_size - 1) // self.block_size
+        dev = self.device
+        gv = dict(
+            input_ids=torch.zeros(max_bs, dtype=torch.int64, device=dev),
+            positions=torch.zeros(max_bs, dtype=torch.int64, device=dev),
+            slot_mapping=torch.full((max_bs,), -1, dtype=torch.int32, device=dev),
+            context_lens=torch.zeros(max_bs, dtype=torch.int32, device=dev),
+            block_tables=torch.zeros(max_bs, max_blocks, dtype=torch.int32, device=dev),
+            outputs=torch.zeros(max_bs, c.hidden_size, dtype=torch.bfloat16, device=dev),
+        )
+        self.graph_bs = [b for b in (1, 2, 4, 8) if b <= max_bs] + list(range(16, max_bs + 1, 16))
+        self.graph_pool = None
+        for bs in reversed(self.graph_bs):
+            graph = torch.cuda.CUDAGraph()
+            set_context(False, slot_mapping=gv["slot_mapping"][:bs], context_lens=gv["context_lens"][:bs], block_tables=gv["block_tables"][:bs])
+            gv["outputs"][:bs] = self.model(gv["input_ids"][:bs], gv["positions"][:bs])  # warm-up (also runs the collectives once)
+            with torch.cuda.graph(graph, self.graph_pool):
+                gv["outputs"][:bs] = self.model(gv["input_ids"][:bs], gv["positions"][:bs])
+            if self.graph_pool is None:
+                self.graph_pool = graph.pool()
+            self.graphs[bs] = graph
+            torch.cuda.synchronize()
+            reset_context()
+        self.graph_vars = gv
+
+
+def sequential_block_tables(lengths: list[int], block_size: int, first_block: int = 0, permutation: list[int] | None = None) -> list[list[int]]:
+    """Block tables for sequences of the given (maximum) lengths, taking blocks
+    in order from `first_block`, or from `permutation` (a shuffled free list)."""
+    tables, nxt = [], first_block
+    for n in lengths:
+        need = (n + block_size - 1) // block_size
+        ids = list(range(nxt, nxt + need))
+        if permutation is not None:
+            ids = [permutation[i] for i in ids]
+        tables.append(ids)
+        nxt += need
+    return tables

@@ -1,0 +1,141 @@
+"""The tcgen05 GEMM, the fused row-parallel launch and the LM head on one B200,
+against the CPU oracle and the golden fixtures."""
+import os
+
+import pytest
+import torch
+
+from oracle import tp_path as O
+from tests.gpu_util import assert_close_bf16, ensure_group, ulp_mismatch_fraction
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def rt(pkg):
+    ensure_group()
+    from nanovllm_b200.runtime import init_runtime, shutdown_runtime
+    r = init_runtime(max_tokens=16384, hidden=5120, oneshot_tokens=1024, vocab=151936, max_seqs=64)
+    yield r
+    shutdown_runtime()
+
+
+@pytest.fixture(scope="module")
+def ops(rt):
+    from nanovllm_b200 import ops as _ops
+    return _ops
+
+
+def _case(m, n, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.02).bfloat16()
+    return x, w
+
+
+GEMM_SHAPES = [
+    (64, 128, 64), (64, 128, 512), (1, 128, 256), (8, 256, 1024), (17, 384, 320), (64, 4096, 4096), (64, 6144, 4096),
+    (33, 1000, 1024), (128, 1024, 1024), (200, 512, 768), (256, 2048, 1024), (257, 1024, 512), (1024, 5120, 1024), (1000, 1032, 520),
+    (2048, 4096, 4096),
+]
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+def test_gemm_against_fp32(ops, rt, m, n, k):
+    x, w = _case(m, n, k, m + n + k)
+    got = ops.gemm(x.to(DEV), w.to(DEV))
+    torch.cuda.synchronize()
+    rt.check_status()
+    ref = x.float() @ w.float().t()
+    assert_close_bf16(got, ref, f"gemm {m}x{n}x{k}")
+    # one rounding of an fp32 accumulation: at most 1 ulp from the oracle's rounding
+    assert ulp_mismatch_fraction(got, O.linear(x, w), 1) < 1e-3
+
+
+def test_gemm_bias_and_strided_input(ops, rt):
+    x, w = _case(48, 512, 256, 5)
+    bias = torch.randn(512).bfloat16()
+    got = ops.gemm(x.to(DEV), w.to(DEV), bias.to(DEV))
+    assert_close_bf16(got, x.float() @ w.float().t() + bias.float(), "gemm+bias (few tokens)")
+    x2, w2 = _case(300, 512, 256, 6)
+    got = ops.gemm(x2.to(DEV), w2.to(DEV), bias.to(DEV))
+    assert_close_bf16(got, x2.float() @ w2.float().t() + bias.float(), "gemm+bias (many tokens)")
+    wide = torch.randn(48, 1024).bfloat16().to(DEV)
+    view = wide[:, 512:768]  # row stride 1024, offset 512 elements
+    assert_close_bf16(ops.gemm(view, w.to(DEV)), view.float().cpu() @ w.float().t(), "gemm strided input")
+
+
+def test_gemm_repeatable_and_counters_clean(ops, rt):
+    """Split tiles are combined through arrival counters that must be back at
+    zero after every launch: the same call twice gives the same result (up to
+    the order in which the fp32 partials of a tile are added, which depends on
+    which CTA arrives last)."""
+    x, w = _case(64, 4096, 12288, 9)
+    a = ops.gemm(x.to(DEV), w.to(DEV))
+    b = ops.gemm(x.to(DEV), w.to(DEV))
+    torch.cuda.synchronize()
+    assert_close_bf16(a, x.float() @ w.float().t(), "gemm 64x4096x12288")
+    assert_close_bf16(b, a.float(), "second launch", abs_tol=2e-3, rel_tol=4e-3)
+
+
+def test_column_parallel_golden(ops, golden_dir):
+    d = torch.load(os.path.join(golden_dir, "col.pt"))
+    for r in range(2):
+        yq = ops.gemm(d["x"].to(DEV), d[f"qkv_w{r}"].to(DEV))
+        yg = ops.gemm(d["x"].to(DEV), d[f"gu_w{r}"].to(DEV))
+        assert ulp_mismatch_fraction(yq, d[f"qkv_y{r}"], 1) < 2e-3
+        assert ulp_mismatch_fraction(yg, d[f"gu_y{r}"], 1) < 2e-3
+
+
+ROWPAR_SHAPES = [(64, 2048, 1024), (64, 3072, 1024), (1, 4096, 4096), (8, 12288, 4096), (64, 4096, 4096), (64, 12288, 4096),
+                 (256, 8192, 5120), (300, 1024, 5120), (1024, 1024, 5120), (1500, 512, 1024)]
+
+
+@pytest.mark.parametrize("m,k,n", ROWPAR_SHAPES)
+def test_rowpar_fused_single_rank(ops, rt, m, k, n):
+    xs, ws, residual, norm_w = O.rowpar_case(m, k, n, 1, seed=m + k)
+    for _ in range(3):  # consecutive launches alternate between the two inboxes
+        normed, new_res = ops.rowpar_fused(xs[0].to(DEV), ws[0].to(DEV), None, residual.to(DEV), norm_w.to(DEV), 1e-6)
+    torch.cuda.synchronize()
+    rt.check_status()
+    exact_n, exact_s = O.fused_row_parallel_norm_exact(xs, ws, residual, norm_w, 1e-6)
+    assert_close_bf16(new_res, exact_s, f"residual {m}x{k}x{n}")
+    assert_close_bf16(normed, exact_n, f"normed {m}x{k}x{n}")
+    ref_n, ref_s = O.fused_row_parallel_norm(xs, ws, residual, norm_w, 1e-6)
+    assert ulp_mismatch_fraction(new_res, ref_s, 1) < 2e-3
+    assert ulp_mismatch_fraction(normed, ref_n, 2) < 2e-3
+
+
+def test_rowpar_plain_forward_and_bias(ops, rt):
+    """norm_w = None is RowParallelLinear.forward: y = x W^T (+ bias)."""
+    xs, ws, _, _ = O.rowpar_case(64, 1024, 1024, 1, seed=4)
+    bias = torch.randn(1024).bfloat16()
+    y = ops.rowpar_fused(xs[0].to(DEV), ws[0].to(DEV), bias.to(DEV), None, None, 0.0)
+    assert_close_bf16(y, xs[0].float() @ ws[0].float().t() + bias.float(), "row-parallel forward + bias")
+
+
+def test_rowpar_golden(ops, rt, golden_dir):
+    """The reference's TP=2 block outputs, reproduced on one rank holding the
+    whole K (the only difference is where the partials are rounded)."""
+    for name in ("rp_a", "rp_b"):
+        d = torch.load(os.path.join(golden_dir, name + ".pt"))
+        normed, new_res = ops.rowpar_fused(d["x_full"].to(DEV), d["w_full"].to(DEV), None, d["residual"].to(DEV), d["norm_w"].to(DEV), 1e-6)
+        assert_close_bf16(new_res, d["new_res"].float(), name + " residual")
+        assert_close_bf16(normed, d["normed"].float(), name + " normed")
+
+
+def test_lm_head_single_rank(ops, rt):
+    g = torch.Generator().manual_seed(2)
+    h = torch.randn(40, 1024, generator=g).bfloat16()
+    w = (torch.randn(151936, 1024, generator=g) * 0.02).bfloat16()
+    logits = ops.lm_head(h.to(DEV), w.to(DEV), None)
+    torch.cuda.synchronize()
+    assert logits.shape == (40, 151936)
+    assert_close_bf16(logits, h.float() @ w.float().t(), "lm_head decode")
+    idx = torch.tensor([4, 5, 16, 39], dtype=torch.int32)
+    logits = ops.lm_head(h.to(DEV), w.to(DEV), idx.to(DEV))
+    torch.cuda.synchronize()
+    assert logits.shape == (4, 151936)
+    assert_close_bf16(logits, h[idx.long()].float() @ w.float().t(), "lm_head prefill (last tokens)")
+    assert torch.equal(ops.argmax(logits).cpu(), logits.float().argmax(-1).cpu())
