@@ -1,0 +1,299 @@
+"""Benchmark of the tensor-parallel layer path: Qwen3-8B decode tokens/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+N > 1 is launched as one process per GPU (torchrun); rank/world come from the
+environment.  Workload: Qwen3-8B, random-init bf16 weights, 64 sequences with
+1024-token uniform-random prompts (prefilled through the same kernels, not
+timed), then K greedy decode steps of the whole batch at tensor-parallel size
+N.  One step = one new token for each of the 64 sequences.
+
+Prints one JSON line (rank 0).  `value`: decode tokens/s with the batch state
+resident on the device (one CUDA graph per step: model, LM head + gather,
+greedy pick, token broadcast, next inputs).  `e2e`: the same through the
+runner's public step() with host-side batch state: pinned host->device copies
+of the step's inputs and a device->host read of the chosen tokens every step.
+
+--impl reference: the reference's own formulation of the layer path (F.linear
++ gloo all_reduce + eager RMSNorm, oracle/cpu_baseline.py) timed on the host
+cores; rank 0 alone runs it.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "qwen3_8b_decode_tokens_per_s"
+BATCH, PROMPT_LEN = 64, 1024
+SHAPE_8B = dict(hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128, intermediate=12288, n_layers=36, vocab=151936)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate_up GEMM launch at TP=1 from the committed ncu summary
+# (profiles/), per tensor-parallel size; None = not captured
+NCU_TRAFFIC_BYTES = {}
+
+
+def workload(tp: int) -> dict:
+    return {"workload": f"Qwen3-8B random-init bf16 decode, batch {BATCH}, {PROMPT_LEN}-token uniform-random prompts, greedy, CUDA graphs, TP={tp}",
+            "batch": BATCH, "prompt_len": PROMPT_LEN, "tp": tp, "kv_block": 256,
+            "l2": "no flush needed: every step streams the rank's whole weight shard (16.4 GB / TP) and the KV cache, far more than the 126 MB L2"}
+
+
+def peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return json.load(open(path)), "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.gpu)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, cell in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def cpu_reference(world: int, warmup: int, steps: int, max_seconds: float) -> dict:
+    """tokens/s of the reference formulation on the host CPU: 64 tokens per
+    decode step, 36 decoder layers per step, one decoder layer per sample."""
+    from oracle import cpu_baseline
+    r = cpu_baseline.time_decoder_layer(SHAPE_8B, BATCH, world, warmup, steps, max_seconds)
+    step_s = r["seconds_per_layer"] * SHAPE_8B["n_layers"]
+    return {"value": BATCH / step_s, "unit": "tok/s", "cores": r["cores"], "kind": "port",
+            "sample": f"{r['steps']} timed passes of ONE decoder layer's tensor-parallel path (qkv, o_proj+all_reduce+add-RMSNorm, gate_up, SiLU*mul, "
+                      f"down_proj+all_reduce+add-RMSNorm) at M={BATCH}, bf16, {world} gloo rank(s) x {r['threads_per_rank']} threads; scaled by 36 layers; "
+                      "attention, embedding and LM head left out",
+            "ms_per_step": step_s * 1e3, "steps": r["steps"]}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    tp = args.gpus
+    steps = max(1, args.steps)
+    ref = cpu_reference(tp, max(1, min(args.warmup, 3)), steps, max_seconds=90.0)
+    line = {"metric": METRIC, "value": ref["value"], "unit": "tok/s", "n_gpus": tp, "steps": ref["steps"], "warmup": max(1, min(args.warmup, 3)),
+            "ms_per_step": ref["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload(tp), "impl": "reference",
+            "cpu_baseline": {k: ref[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": ref["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_b200(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as entry
+    entry.load_package()
+    from nanovllm_b200 import _abi, ops
+    from nanovllm_b200.engine.model_runner import QWEN3_8B, ModelConfig, ModelRunner, ResidentDecoder, Seq, sequential_block_tables
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch N>1 with torchrun"
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29577")
+    torch.cuda.set_device(local)
+    dist.init_process_group("cpu:gloo,cuda:nccl" if world > 1 else "gloo", rank=rank, world_size=world)
+    dev = torch.device("cuda", local)
+    K, W = args.steps, max(3, args.warmup)
+    max_len = ((PROMPT_LEN + K + W + 8 + 255) // 256) * 256
+    blocks_per_seq = max_len // 256
+    runner = ModelRunner(ModelConfig(**QWEN3_8B), max_num_seqs=BATCH, max_model_len=max_len, max_num_batched_tokens=16384,
+                         num_kvcache_blocks=BATCH * blocks_per_seq, oneshot_tokens=1024, seed=0)
+    resident = ResidentDecoder(runner, BATCH)
+
+    # ---- prompts and prefill (not timed): 4 steps of 16 sequences, as the reference's scheduler would batch them
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, SHAPE_8B["vocab"], (BATCH, PROMPT_LEN), generator=g).tolist()
+    tables = sequential_block_tables([max_len] * BATCH, 256)
+    first = []
+    for i in range(0, BATCH, 16):
+        first += runner.step([Seq(list(p), bt) for p, bt in zip(prompts[i:i + 16], tables[i:i + 16])], True)
+
+    def fresh_seqs():
+        return [Seq(list(p) + [t], bt) for p, t, bt in zip(prompts, first, tables)]
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident decode: `value` ----
+    resident.load(fresh_seqs())
+    for _ in range(W):
+        resident.replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        e0.record()
+        for _ in range(K):
+            resident.replay()
+        e1.record()
+        barrier()
+    total_ms = max_over_ranks(e0.elapsed_time(e1))
+    runner.runtime.check_status()
+    launches = K * resident.kernels_per_step
+    final_tokens = resident.tokens.tolist()
+    assert all(0 <= t < SHAPE_8B["vocab"] for t in final_tokens)
+
+    # ---- end to end through runner.step(): host batch state, H2D inputs + D2H tokens every step ----
+    seqs = fresh_seqs()
+    def e2e_step():
+        toks = runner.step(seqs, False)
+        for s, t in zip(seqs, toks):
+            s.token_ids.append(t)
+    for _ in range(W):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(K):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+    h2d = BATCH * (8 + 8 + 4 + 4) + BATCH * blocks_per_seq * 4
+    d2h = BATCH * 8
+
+    # ---- roofline of the dominant kernel: the gate_up GEMM (largest share of the step), timed alone ----
+    pk, pk_kind = peaks()
+    layers = runner.model.model.layers
+    x = torch.randn(BATCH, SHAPE_8B["hidden"], device=dev).bfloat16()
+    n_local = 2 * SHAPE_8B["intermediate"] // world
+    for i in range(8):
+        ops.gemm(x, layers[i % len(layers)].mlp.gate_up_proj.weight)
+    iters = 4 * len(layers)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(iters):  # a different layer's weight every launch: 36 x 201 MB / TP, never L2-resident
+        ops.gemm(x, layers[i % len(layers)].mlp.gate_up_proj.weight)
+    e1.record()
+    torch.cuda.synchronize()
+    k_us = e0.elapsed_time(e1) * 1e3 / iters
+    alg_bytes = 2.0 * (BATCH * SHAPE_8B["hidden"] + n_local * SHAPE_8B["hidden"] + BATCH * n_local)
+    achieved = alg_bytes / (k_us * 1e-6) / 1e9
+    roofline = {"bound": "hbm", "kernel": f"gemm_kernel<BN=64,SWAP> gate_up_proj M={BATCH} N={n_local} K={SHAPE_8B['hidden']}", "achieved": achieved,
+                "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_kind": pk_kind + " (burst copy bandwidth)",
+                "us_per_launch": k_us, "algorithmic_bytes": alg_bytes, "traffic": NCU_TRAFFIC_BYTES.get(world)}
+    # the whole step against the HBM bound: weights of the rank + KV read at the mean context length
+    c = SHAPE_8B
+    w_bytes = 2.0 * (c["n_layers"] * (c["hidden"] * (c["n_heads"] + 2 * c["n_kv_heads"]) * c["head_dim"] + c["hidden"] * c["n_heads"] * c["head_dim"]
+                                      + 3 * c["hidden"] * c["intermediate"]) + c["vocab"] * c["hidden"]) / world
+    kv_bytes = 2.0 * 2 * c["n_layers"] * BATCH * (PROMPT_LEN + W + K / 2) * c["n_kv_heads"] * c["head_dim"] / world
+    step_ms = total_ms / K
+    step_roof = {"bound": "hbm", "achieved": (w_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                 "frac": (w_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9 / pk["hbm_gbs"], "bytes_per_step": w_bytes + kv_bytes}
+
+    # ---- the fused row-parallel block next to F.linear + NCCL all_reduce + RMSNorm (N > 1) ----
+    block_cmp = None
+    if world > 1 and not args.skip_nccl:
+        try:
+            from nanovllm_b200 import rowpar_microbench as mb
+            block_cmp = mb.compare_blocks([("o_proj", BATCH, c["hidden"], c["n_heads"] * c["head_dim"] // world),
+                                           ("down_proj", BATCH, c["hidden"], c["intermediate"] // world)], pk, iters=200)
+        except Exception as ex:  # the comparison is informative only
+            block_cmp = {"error": repr(ex)[:200]}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        ref = cpu_reference(1, 1, 64, max_seconds=15.0)
+        cpu = {k: ref[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": BATCH * K / (total_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": workload(world), "clocks": clocks.summary(),
+                "e2e": {"value": BATCH * K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / K},
+                "gpu_launches": launches, "roofline": roofline, "step_roofline": step_roof, "cpu_baseline": cpu}
+        if block_cmp is not None:
+            line["rowpar_block_us"] = block_cmp
+        print(json.dumps(line), flush=True)
+    runner.exit()
+    dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg")
+    ap.add_argument("--skip-nccl", action="store_true", help="omit the NCCL comparison of the row-parallel block")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -156,6 +156,27 @@ int b2_embed(b2_ctx* ctx, const int64_t* ids, const void* W, int64_t vocab_start
 int b2_lm_head(b2_ctx* ctx, const void* h, int64_t ldh, const int32_t* row_index, const void* W, int64_t ldw,
                int B, int Vr, int H, void** logits_out, void* stream);
 
+/* ---- sampled-token broadcast: replaces the data the reference ships from
+ *      rank 0 to the other ranks inside its pickled "run" message
+ *      (nanovllm/engine/model_runner.py:76-89: the next step's last_token of
+ *      every sequence) ---------------------------------------------------------
+ * buf: int64 [n] on every rank, n <= max_seqs, values >= 0.  Rank 0's values
+ * are written into every other rank's buf by the end of the call's kernel.
+ * No-op when world == 1. */
+int b2_broadcast_tokens(b2_ctx* ctx, int64_t* buf, int n, void* stream);
+
+/* ---- next decode step's inputs, computed on the device: what
+ *      ModelRunner.prepare_decode builds on the host every step
+ *      (nanovllm/engine/model_runner.py:172-188) -------------------------------
+ * For i < n: input_ids[i] = tokens[i]; positions[i] += 1; context_lens[i] += 1;
+ * slot_mapping[i] = block_tables[i, positions[i] / block_size] * block_size
+ *                   + positions[i] % block_size.  block_tables int32 with row
+ * stride bt_stride.  Lets consecutive decode steps run without a host round
+ * trip. */
+int b2_advance_decode(const int64_t* tokens, int64_t* input_ids, int64_t* positions, int32_t* context_lens,
+                      int32_t* slot_mapping, const int32_t* block_tables, int64_t bt_stride, int block_size,
+                      int n, void* stream);
+
 /* ---- elementwise neighbours of the path (the reference generates these with
  *      torch.compile -> Triton) ----------------------------------------------
  * SiluAndMul.forward (nanovllm/layers/activation.py:8-11):

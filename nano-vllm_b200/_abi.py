@@ -25,7 +25,8 @@ _ERR_NAMES = {1: "bad argument", 2: "shape outside what the context was created 
               4: "bad state (peers not imported?)", 5: "device-side wait timed out", 6: "unsupported"}
 WAIT_NAMES = {0: "none", 1: "GEMM: TMA stage never filled", 2: "GEMM: stage never freed", 3: "GEMM: accumulator never completed",
               4: "GEMM: accumulator never drained", 5: "fused row-parallel: partial rows never arrived",
-              6: "embedding: owner row never arrived", 7: "LM head: a peer's logits never arrived"}
+              6: "embedding: owner row never arrived", 7: "LM head: a peer's logits never arrived",
+              8: "token broadcast: rank 0's tokens never arrived"}
 
 
 class Config(C.Structure):
@@ -55,6 +56,8 @@ SIGNATURES = {
     "b2_silu_and_mul": [_p, _i64, _i, _i, _p, _p],
     "b2_qk_norm_rope_store": [_p, _i64, _i, _i, _i, _i, _p, _p, _f, _p, _p, _p, _p, _p, _p],
     "b2_argmax": [_p, _i64, _i, _i, _p, _p],
+    "b2_broadcast_tokens": [_p, _p, _i, _p],
+    "b2_advance_decode": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _p],
 }
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)

@@ -20,7 +20,8 @@ enum : int {
   B2_WAIT_TMEM_EMPTY = 4,   // MMA warp waiting for a drained accumulator
   B2_WAIT_PARTIALS = 5,     // fused reduce waiting for partial rows (local or peer)
   B2_WAIT_EMBED = 6,        // embedding waiting for the owner rank's row
-  B2_WAIT_LOGITS = 7        // rank 0 waiting for peers' logits slices
+  B2_WAIT_LOGITS = 7,       // rank 0 waiting for peers' logits slices
+  B2_WAIT_TOKENS = 8        // a rank waiting for rank 0's sampled tokens
 };
 
 // The bf16 bit pattern that marks "not written yet" in data-as-flag buffers:
@@ -36,7 +37,8 @@ struct B2DeviceState {
   unsigned int embed_done;
   unsigned int lmhead_seq;
   unsigned int lmhead_done;
-  unsigned int pad[2];
+  unsigned int bcast_seq;
+  unsigned int pad;
 };
 
 // Host-visible (mapped, pinned) status word.
@@ -269,6 +271,7 @@ struct b2_ctx {
   size_t off_embed;     // [2 parity][max_tokens][hidden] bf16
   size_t off_logits;    // [max_seqs][vocab] bf16 (used on rank 0)
   size_t off_flags;     // [world] uint32 arrival flags for the logits gather
+  size_t off_tokens;    // [2 parity][max_seqs] int64 token inbox, -1 = not written
 
   // rank-local scratch
   float* splitk_ws;     // stream-K partial accumulators

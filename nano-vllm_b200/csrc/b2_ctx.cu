@@ -98,6 +98,8 @@ int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
   if (c->cfg.vocab > 0 && c->cfg.max_seqs > 0) off = align_up(off + static_cast<size_t>(c->cfg.max_seqs) * c->cfg.vocab * 2, 1024);
   c->off_flags = off;
   off = align_up(off + 256, 1024);
+  c->off_tokens = off;
+  off = align_up(off + 2 * static_cast<size_t>(c->cfg.max_seqs > 0 ? c->cfg.max_seqs : 1) * 8, 1024);
   c->symm_bytes = off;
   B2_CUDA(cudaMalloc(&c->symm, c->symm_bytes));
   // data-as-flag buffers start out "not written"; flags start at zero
@@ -106,7 +108,8 @@ int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
     b2_fill_u32_kernel<<<1024, 256>>>(reinterpret_cast<uint32_t*>(c->symm), words, B2_SENTINEL32);
     b2::count_launch();
     B2_CUDA(cudaGetLastError());
-    B2_CUDA(cudaMemset(c->symm + c->off_logits, 0, c->symm_bytes - c->off_logits));
+    B2_CUDA(cudaMemset(c->symm + c->off_logits, 0, c->off_tokens - c->off_logits));
+    B2_CUDA(cudaMemset(c->symm + c->off_tokens, 0xFF, c->symm_bytes - c->off_tokens));
   }
   for (int r = 0; r < B2_MAX_WORLD; ++r) c->peer[r] = nullptr;
   c->peer[c->cfg.rank] = c->symm;

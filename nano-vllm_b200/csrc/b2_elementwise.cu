@@ -349,6 +349,66 @@ __global__ void __launch_bounds__(256) argmax_kernel(const uint16_t* __restrict_
   }
 }
 
+// ---------------------------------------------------------------------------
+// Rank 0's int64 values to every rank.  The inbox holds -1 until a value lands;
+// the reader copies it out and puts -1 back.  Two inboxes alternate by call.
+// One block; n <= max_seqs.
+// ---------------------------------------------------------------------------
+struct BcastArgs {
+  int64_t* buf;
+  int n, world, rank;
+  unsigned char* inbox[B2_MAX_WORLD];
+  size_t parity_stride;
+  B2DeviceState* dstate;
+  B2Status* status;
+  uint64_t timeout_ns;
+};
+
+__global__ void __launch_bounds__(256) broadcast_tokens_kernel(const BcastArgs a) {
+  const unsigned int parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->bcast_seq) & 1u;
+  for (int i = threadIdx.x; i < a.n; i += blockDim.x) {
+    if (a.rank == 0) {
+      const long long v = a.buf[i];
+      for (int r = 1; r < a.world; ++r)
+        *reinterpret_cast<volatile long long*>(a.inbox[r] + parity * a.parity_stride + i * 8) = v;
+    } else {
+      volatile long long* src = reinterpret_cast<volatile long long*>(a.inbox[a.rank] + parity * a.parity_stride + i * 8);
+      long long v = *src;
+      if (v < 0) {
+        const uint64_t t0 = b2::globaltimer_ns();
+        for (uint32_t it = 1; (v = *src) < 0; ++it) {
+          if ((it & 0xFF) == 0 && b2::globaltimer_ns() - t0 > a.timeout_ns) {
+            b2::report_timeout(a.status, B2_WAIT_TOKENS);
+            v = 0;
+            break;
+          }
+        }
+      }
+      a.buf[i] = v;
+      *src = -1;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    a.dstate->bcast_seq += 1;
+    __threadfence();
+  }
+}
+
+__global__ void advance_decode_kernel(const int64_t* __restrict__ tokens, int64_t* __restrict__ input_ids,
+                                      int64_t* __restrict__ positions, int32_t* __restrict__ context_lens,
+                                      int32_t* __restrict__ slot_mapping, const int32_t* __restrict__ block_tables,
+                                      int64_t bt_stride, int block_size, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  input_ids[i] = tokens[i];
+  const int64_t p = positions[i] + 1;
+  positions[i] = p;
+  context_lens[i] += 1;
+  const int32_t blk = block_tables[i * bt_stride + p / block_size];
+  slot_mapping[i] = blk * block_size + static_cast<int32_t>(p % block_size);
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 int grid_for(int64_t work_items, int threads, int cap) {
   int64_t g = (work_items + threads - 1) / threads;
@@ -474,6 +534,37 @@ int b2_embed(b2_ctx* ctx, const int64_t* ids, const void* W, int64_t vocab_start
   const int cap = ctx ? ctx->num_sms * 4 : 148 * 4;
   const int grid = grid_for(static_cast<int64_t>(M) * (H / 8), 256, cap);
   embed_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  b2::count_launch();
+  B2_CUDA(cudaGetLastError());
+  return B2_OK;
+}
+
+int b2_broadcast_tokens(b2_ctx* ctx, int64_t* buf, int n, void* stream) {
+  if (ctx == nullptr || n < 0) return B2_ERR_ARG;
+  if (ctx->cfg.world == 1 || n == 0) return B2_OK;
+  if (buf == nullptr) return B2_ERR_ARG;
+  if (!ctx->peers_ready) return B2_ERR_STATE;
+  if (n > ctx->cfg.max_seqs) return B2_ERR_SHAPE;
+  BcastArgs a{};
+  a.buf = buf; a.n = n; a.world = ctx->cfg.world; a.rank = ctx->cfg.rank;
+  for (int r = 0; r < a.world; ++r) a.inbox[r] = ctx->peer[r] + ctx->off_tokens;
+  a.parity_stride = static_cast<size_t>(ctx->cfg.max_seqs) * 8;
+  a.dstate = ctx->dstate;
+  a.status = ctx->status_dev;
+  a.timeout_ns = static_cast<uint64_t>(ctx->cfg.timeout_ms) * 1000000ull;
+  broadcast_tokens_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  b2::count_launch();
+  B2_CUDA(cudaGetLastError());
+  return B2_OK;
+}
+
+int b2_advance_decode(const int64_t* tokens, int64_t* input_ids, int64_t* positions, int32_t* context_lens,
+                      int32_t* slot_mapping, const int32_t* block_tables, int64_t bt_stride, int block_size, int n, void* stream) {
+  if (n < 0 || block_size <= 0) return B2_ERR_ARG;
+  if (n == 0) return B2_OK;
+  if (!tokens || !input_ids || !positions || !context_lens || !slot_mapping || !block_tables) return B2_ERR_ARG;
+  advance_decode_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(tokens, input_ids, positions, context_lens,
+                                                                                       slot_mapping, block_tables, bt_stride, block_size, n);
   b2::count_launch();
   B2_CUDA(cudaGetLastError());
   return B2_OK;

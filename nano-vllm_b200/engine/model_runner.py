@@ -196,18 +196,20 @@ class ModelRunner:
 
     @torch.inference_mode()
     def step(self, seqs: list[Seq], is_prefill: bool, temperatures: list[float] | None = None, num_new: list[int] | None = None):
-        """One forward pass + sampling.  Returns the new token ids on rank 0
-        (None elsewhere).  temperatures=None means greedy (argmax)."""
+        """One forward pass + sampling on rank 0; the chosen token ids are
+        returned on every rank.  temperatures=None means greedy (argmax)."""
         ids, pos = self.prepare_prefill(seqs, num_new) if is_prefill else self.prepare_decode(seqs)
         logits = self.run_model(ids, pos, is_prefill)
-        tokens = None
+        picked = torch.zeros(len(seqs), dtype=torch.int64, device=self.device)
         if self.rank == 0:
             if temperatures is None:
-                tokens = Sampler.greedy(logits).tolist()
+                picked = Sampler.greedy(logits)
             else:
-                tokens = self.sampler(logits, self._h2d(temperatures, torch.float32)).tolist()
-        else:
-            torch.cuda.current_stream().synchronize()
+                picked = self.sampler(logits, self._h2d(temperatures, torch.float32))
+        if self.world > 1:
+            from .. import ops
+            ops.broadcast_tokens(picked)  # rank 0's choice reaches every rank on the device
+        tokens = picked.tolist()  # the step's synchronisation point
         reset_context()
         self.runtime.check_status()
         return tokens
@@ -241,6 +243,63 @@ class ModelRunner:
             torch.cuda.synchronize()
             reset_context()
         self.graph_vars = gv
+
+
+class ResidentDecoder:
+    """Decode steps that never leave the device: one CUDA graph holds the model
+    forward, the LM head with its gather, the greedy pick on rank 0, the token
+    broadcast to the other ranks and the computation of the next step's inputs
+    (what nanovllm/engine/model_runner.py:172-188 and :195-212 do with a host
+    round trip every step).  `load(seqs)` puts a batch on the device;
+    `replay()` advances every sequence by one token."""
+
+    @torch.inference_mode()
+    def __init__(self, runner: ModelRunner, batch: int):
+        from .. import ops
+        assert not runner.enforce_eager and batch in runner.graphs, "batch must be one of the captured decode batch sizes"
+        self.r, self.bs, self.ops = runner, batch, ops
+        self.tokens = torch.zeros(batch, dtype=torch.int64, device=runner.device)
+        gv = runner.graph_vars
+        gv["slot_mapping"].fill_(-1)
+        gv["context_lens"].zero_()
+        before = ops._abi.launch_count()
+        self._body()  # warm-up: also creates the logits view outside the capture
+        self.kernels_per_step = ops._abi.launch_count() - before
+        gv["slot_mapping"].fill_(-1)
+        gv["context_lens"].zero_()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, runner.graph_pool):
+            self._body()
+        torch.cuda.synchronize()
+
+    @torch.inference_mode()
+    def _body(self):
+        r, bs, gv = self.r, self.bs, self.r.graph_vars
+        set_context(False, slot_mapping=gv["slot_mapping"][:bs], context_lens=gv["context_lens"][:bs], block_tables=gv["block_tables"][:bs])
+        logits = r.model.compute_logits(r.model(gv["input_ids"][:bs], gv["positions"][:bs]))
+        if r.rank == 0:
+            self.ops.argmax(logits, self.tokens)
+        if r.world > 1:
+            self.ops.broadcast_tokens(self.tokens)
+        self.ops.advance_decode(self.tokens, gv["input_ids"], gv["positions"], gv["context_lens"], gv["slot_mapping"],
+                                gv["block_tables"], r.block_size)
+        reset_context()
+
+    @torch.inference_mode()
+    def load(self, seqs: list[Seq]) -> None:
+        """The batch's state as prepare_decode would build it for the next step."""
+        r, gv, n = self.r, self.r.graph_vars, len(seqs)
+        assert n == self.bs
+        bs = r.block_size
+        width = max(len(s.block_table) for s in seqs)
+        gv["input_ids"][:n] = r._h2d([s.token_ids[-1] for s in seqs], torch.int64)
+        gv["positions"][:n] = r._h2d([len(s) - 1 for s in seqs], torch.int64)
+        gv["context_lens"][:n] = r._h2d([len(s) for s in seqs], torch.int32)
+        gv["slot_mapping"][:n] = r._h2d([s.block_table[(len(s) - 1) // bs] * bs + (len(s) - 1) % bs for s in seqs], torch.int32)
+        gv["block_tables"][:n, :width] = r._h2d([s.block_table + [0] * (width - len(s.block_table)) for s in seqs], torch.int32)
+
+    def replay(self) -> None:
+        self.graph.replay()
 
 
 def sequential_block_tables(lengths: list[int], block_size: int, first_block: int = 0, permutation: list[int] | None = None) -> list[list[int]]:

@@ -154,6 +154,9 @@ class _DevicePtr:
         self.__cuda_array_interface__ = {"shape": shape, "typestr": "<u2", "data": (ptr, False), "version": 3, "strides": None}
 
 
+_LOGIT_VIEWS: dict = {}
+
+
 def lm_head(h: torch.Tensor, w: torch.Tensor, row_index: torch.Tensor | None):
     """Returns the gathered [B, vocab] logits on rank 0 (a view of the runtime's
     buffer, valid until the next call) and None elsewhere."""
@@ -171,12 +174,34 @@ def lm_head(h: torch.Tensor, w: torch.Tensor, row_index: torch.Tensor | None):
     if rt.rank != 0:
         return None
     vocab = Vr * rt.world
-    raw = torch.as_tensor(_DevicePtr(out.value, (B, vocab)), device=h.device)
-    return raw.view(torch.bfloat16)
+    key = (out.value, B, vocab)
+    view = _LOGIT_VIEWS.get(key)
+    if view is None:  # built once per shape (outside any graph capture: the first call of a shape is a warm-up)
+        view = torch.as_tensor(_DevicePtr(out.value, (B, vocab)), device=h.device).view(torch.bfloat16)
+        _LOGIT_VIEWS[key] = view
+    return view
 
 
-def argmax(logits: torch.Tensor) -> torch.Tensor:
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     assert logits.dim() == 2 and logits.dtype == torch.bfloat16 and logits.stride(1) == 1
-    out = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
+    if out is None:
+        out = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
+    assert out.dtype == torch.int64 and out.numel() >= logits.shape[0]
     _abi.check(_lib.b2_argmax(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], out.data_ptr(), _stream()), "b2_argmax")
     return out
+
+
+def broadcast_tokens(buf: torch.Tensor) -> torch.Tensor:
+    """Rank 0's int64 token ids into `buf` on every rank (in place)."""
+    assert buf.dtype == torch.int64 and buf.is_cuda and buf.is_contiguous()
+    _abi.check(_lib.b2_broadcast_tokens(get_runtime().ctx, buf.data_ptr(), buf.numel(), _stream()), "b2_broadcast_tokens")
+    return buf
+
+
+def advance_decode(tokens, input_ids, positions, context_lens, slot_mapping, block_tables, block_size: int) -> None:
+    """Device-side equivalent of building the next decode step's inputs."""
+    n = tokens.numel()
+    assert tokens.dtype == torch.int64 and positions.dtype == torch.int64 and block_tables.dtype == torch.int32
+    _abi.check(_lib.b2_advance_decode(tokens.data_ptr(), input_ids.data_ptr(), positions.data_ptr(), context_lens.data_ptr(),
+                                      slot_mapping.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), block_size, n, _stream()),
+               "b2_advance_decode")

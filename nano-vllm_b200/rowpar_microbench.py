@@ -1,0 +1,157 @@
+"""Microbenchmark of the fused row-parallel block (GEMM + cross-GPU reduction +
+residual add + RMSNorm in one launch) next to the reference's formulation of
+the same block on the same GPUs: F.linear, NCCL all_reduce
+(nanovllm/layers/linear.py:153-155) and the torch.compile'd add + RMSNorm
+(nanovllm/layers/layernorm.py:28-40).
+
+Both sides run inside CUDA graphs, as the decode path does, over a rotation of
+weight copies larger than L2, and are timed with CUDA events (max over ranks).
+
+Stand-alone, under torchrun with N ranks, it runs the Qwen3-32B shapes
+(hidden 5120; o_proj K = 8192, down_proj K = 25600, split over N) for
+M in {1, 8, 64, 256, 1024, 8192} and prints one JSON row per case:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        nano-vllm_b200/rowpar_microbench.py [--m 1,8,64] [--no-nccl]
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool (nominal 900)
+
+
+def roofline_us(m: int, n: int, kr: int, world: int, peaks: dict) -> dict:
+    flops = 2.0 * m * n * kr
+    nvl = 2.0 * (world - 1) / world * m * n * 2
+    hbm = 2.0 * (m * kr + n * kr + 3 * m * n + n)
+    t = {"flops_us": flops / (peaks["bf16_tflops"] * 1e12) * 1e6, "nvlink_us": nvl / (NVLINK_GBS * 1e9) * 1e6,
+         "hbm_us": hbm / (peaks["hbm_gbs"] * 1e9) * 1e6}
+    t["roof_us"] = max(t["flops_us"], t["nvlink_us"], t["hbm_us"])
+    t["roof2_us"] = max(t["flops_us"], t["nvlink_us"])  # "the slower of compute at peak and bytes over NVLink"
+    return t
+
+
+def _max_over_ranks(v: float) -> float:
+    if not dist.is_initialized() or dist.get_world_size() == 1:
+        return v
+    t = torch.tensor([v], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_in_graph(make_call, n_variants: int, iters: int) -> float:
+    """make_call(i) issues the i-th variant of the call on the current stream.
+    One CUDA graph holds n_variants calls; returns microseconds per call."""
+    for i in range(min(n_variants, 3)):
+        make_call(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(n_variants):
+            make_call(i)
+    replays = max(1, iters // n_variants)
+    graph.replay()
+    torch.cuda.synchronize()
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return _max_over_ranks(e0.elapsed_time(e1) * 1e3 / (replays * n_variants))
+
+
+def _reference_add_rms(x, residual, weight, eps):
+    orig = x.dtype
+    x = x.float().add_(residual.float())
+    residual = x.to(orig)
+    var = x.pow(2).mean(dim=-1, keepdim=True)
+    x.mul_(torch.rsqrt(var + eps))
+    return x.to(orig).mul_(weight), residual
+
+
+def compare_blocks(blocks, peaks: dict, iters: int = 200, with_nccl: bool = True) -> dict:
+    from . import ops
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = {}
+    norm_fn = _reference_add_rms
+    if with_nccl:
+        try:
+            norm_fn = torch.compile(_reference_add_rms)
+        except Exception:
+            norm_fn = _reference_add_rms
+    for name, m, n, kr in blocks:
+        n_w = int(max(2, min(64, (300 << 20) // (n * kr * 2) + 1)))
+        ws = [(torch.randn(n, kr, device=dev) * 0.02).bfloat16() for _ in range(n_w)]
+        x = torch.randn(m, kr, device=dev).bfloat16()
+        residual = torch.randn(m, n, device=dev).bfloat16()
+        norm_w = (torch.rand(n, device=dev) + 0.5).bfloat16()
+        ours = time_in_graph(lambda i: ops.rowpar_fused(x, ws[i % n_w], None, residual, norm_w, 1e-6), n_w, iters)
+        row = {"M": m, "N": n, "Kr": kr, "tp": world, "b200_us": ours}
+        row.update(roofline_us(m, n, kr, world, peaks))
+        row["frac_of_roof"] = row["roof_us"] / ours
+        if with_nccl and world > 1:
+            def ref_call(i):
+                y = F.linear(x, ws[i % n_w])
+                dist.all_reduce(y)
+                return norm_fn(y, residual, norm_w, 1e-6)
+            try:
+                row["nccl_us"] = time_in_graph(ref_call, n_w, iters)
+                row["speedup_vs_nccl"] = row["nccl_us"] / ours
+            except Exception as ex:
+                row["nccl_error"] = repr(ex)[:160]
+        out[name] = row
+        del ws
+        torch.cuda.empty_cache()
+    return out
+
+
+def main():
+    import argparse
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, os.path.dirname(here))
+    import __graft_entry__ as entry
+    entry.load_package()
+    from nanovllm_b200.runtime import init_runtime, shutdown_runtime
+    from nanovllm_b200 import rowpar_microbench as mb  # the package-relative copy of this module
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", default="1,8,64,256,1024,8192")
+    ap.add_argument("--no-nccl", action="store_true")
+    ap.add_argument("--iters", type=int, default=200)
+    a = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29578")
+    torch.cuda.set_device(local)
+    dist.init_process_group("cpu:gloo,cuda:nccl" if world > 1 else "gloo", rank=rank, world_size=world)
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    p = os.path.join(os.path.dirname(here), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        peaks = json.load(open(p))
+    ms = [int(v) for v in a.m.split(",")]
+    init_runtime(max_tokens=max(ms), hidden=5120, oneshot_tokens=1024)
+    try:
+        for proj, k_total in (("o_proj", 8192), ("down_proj", 25600)):
+            for m in ms:
+                res = mb.compare_blocks([(proj, m, 5120, k_total // world)], peaks, iters=a.iters if m <= 1024 else 20, with_nccl=not a.no_nccl)
+                if rank == 0:
+                    print(json.dumps(res[proj] | {"proj": proj}), flush=True)
+    finally:
+        shutdown_runtime()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -48,6 +48,8 @@ class TPRuntime:
 
     def close(self) -> None:
         if self.ctx:
+            from . import ops
+            ops._LOGIT_VIEWS.clear()  # views of the buffer that is about to be freed
             torch.cuda.synchronize()
             _abi.lib.b2_ctx_destroy(self.ctx)
             self.ctx = None
