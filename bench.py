@@ -39,7 +39,7 @@ SHAPE_8B = dict(hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128, intermediat
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate_up GEMM launch at TP=1 from the committed ncu summary
 # (profiles/), per tensor-parallel size; None = not captured
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {1: 208.6e6}
 
 
 def workload(tp: int) -> dict:
@@ -194,11 +194,13 @@ def run_b200(args) -> None:
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
+        torch.cuda.nvtx.range_push("timed")
         e0.record()
         for _ in range(K):
             resident.replay()
         e1.record()
         barrier()
+        torch.cuda.nvtx.range_pop()
     total_ms = max_over_ranks(e0.elapsed_time(e1))
     runner.runtime.check_status()
     launches = K * resident.kernels_per_step
@@ -228,16 +230,10 @@ def run_b200(args) -> None:
     layers = runner.model.model.layers
     x = torch.randn(BATCH, SHAPE_8B["hidden"], device=dev).bfloat16()
     n_local = 2 * SHAPE_8B["intermediate"] // world
-    for i in range(8):
-        ops.gemm(x, layers[i % len(layers)].mlp.gate_up_proj.weight)
-    iters = 4 * len(layers)
-    torch.cuda.synchronize()
-    e0.record()
-    for i in range(iters):  # a different layer's weight every launch: 36 x 201 MB / TP, never L2-resident
-        ops.gemm(x, layers[i % len(layers)].mlp.gate_up_proj.weight)
-    e1.record()
-    torch.cuda.synchronize()
-    k_us = e0.elapsed_time(e1) * 1e3 / iters
+    # one CUDA graph holds one launch per layer's weight (36 x 201 MB / TP: never L2-resident), so the host is out of the loop
+    from nanovllm_b200.rowpar_microbench import time_in_graph
+    with torch.inference_mode():
+        k_us = time_in_graph(lambda i: ops.gemm(x, layers[i % len(layers)].mlp.gate_up_proj.weight), len(layers), 6 * len(layers))
     alg_bytes = 2.0 * (BATCH * SHAPE_8B["hidden"] + n_local * SHAPE_8B["hidden"] + BATCH * n_local)
     achieved = alg_bytes / (k_us * 1e-6) / 1e9
     roofline = {"bound": "hbm", "kernel": f"gemm_kernel<BN=64,SWAP> gate_up_proj M={BATCH} N={n_local} K={SHAPE_8B['hidden']}", "achieved": achieved,

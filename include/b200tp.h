@@ -78,6 +78,16 @@ int b2_ctx_destroy(b2_ctx* ctx);
 int b2_status(b2_ctx* ctx, int* code, int* detail);
 int b2_status_clear(b2_ctx* ctx);
 
+/* Phase tracing of the GEMM / fused row-parallel kernel (the reference has
+ * only per-step wall-clock in nanovllm/engine/llm_engine.py:72-83).  While
+ * enabled, every CTA of those kernels records 8 (SM clock, global ns) stamps:
+ * 0 start, 1 first operand tile landed, 2 last MMA issued, 3 last accumulator
+ * complete, 4 epilogue done, 5 GEMM part left, 6 reduce phase done.  If
+ * host_out is non-NULL the call synchronises the device, copies
+ * min(max_ctas, SM count) * 16 uint64 stamps of the most recent launch and
+ * clears them.  Not for use during graph capture. */
+int b2_trace(b2_ctx* ctx, int enable, unsigned long long* host_out, int max_ctas);
+
 /* Message of the last failed CUDA call made by this library on this thread. */
 const char* b2_last_error(void);
 

@@ -282,6 +282,8 @@ struct b2_ctx {
   B2Status* status_host;  // mapped pinned host memory
   B2Status* status_dev;   // device alias of status_host
   __nv_bfloat16* gather_rows;  // [max_seqs][hidden] staging for the LM head
+  unsigned long long* trace;   // [num_sms][8][2] phase stamps of the last GEMM launch
+  bool trace_on;
 };
 
 namespace b2 {

@@ -128,6 +128,9 @@ int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
   c->status_host->rank = c->cfg.rank;
   B2_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&c->status_dev), c->status_host, 0));
   if (c->cfg.max_seqs > 0) B2_CUDA(cudaMalloc(&c->gather_rows, static_cast<size_t>(c->cfg.max_seqs) * H * 2));
+  B2_CUDA(cudaMalloc(&c->trace, static_cast<size_t>(c->num_sms) * 16 * sizeof(unsigned long long)));
+  B2_CUDA(cudaMemset(c->trace, 0, static_cast<size_t>(c->num_sms) * 16 * sizeof(unsigned long long)));
+  c->trace_on = false;
   B2_CUDA(cudaDeviceSynchronize());
   *out = c;
   return B2_OK;
@@ -167,6 +170,7 @@ int b2_ctx_destroy(b2_ctx* c) {
   cudaFree(c->splitk_ws);
   cudaFree(c->tile_counters);
   cudaFree(c->dstate);
+  cudaFree(c->trace);
   if (c->gather_rows) cudaFree(c->gather_rows);
   cudaFreeHost(c->status_host);
   delete c;
@@ -178,6 +182,18 @@ int b2_status(b2_ctx* c, int* code, int* detail) {
   const volatile B2Status* s = c->status_host;
   if (code) *code = s->code;
   if (detail) *detail = s->detail;
+  return B2_OK;
+}
+
+int b2_trace(b2_ctx* c, int enable, unsigned long long* host_out, int max_ctas) {
+  if (c == nullptr) return B2_ERR_ARG;
+  if (host_out != nullptr) {
+    const int n = max_ctas < c->num_sms ? max_ctas : c->num_sms;
+    B2_CUDA(cudaDeviceSynchronize());
+    B2_CUDA(cudaMemcpy(host_out, c->trace, static_cast<size_t>(n) * 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    B2_CUDA(cudaMemset(c->trace, 0, static_cast<size_t>(c->num_sms) * 16 * sizeof(unsigned long long)));
+  }
+  c->trace_on = enable != 0;
   return B2_OK;
 }
 

@@ -60,6 +60,7 @@ struct GemmArgs {
   uint16_t* residual_out;
   B2DeviceState* dstate;
   uint64_t timeout_ns;
+  unsigned long long* trace;  // optional [CTA][8][2] (SM clock, global ns) phase stamps; null = off
 };
 
 template <int BN>
@@ -260,6 +261,14 @@ __device__ __forceinline__ void reduce_rows(const GemmArgs& a, unsigned int pari
   }
 }
 
+__device__ __forceinline__ void stamp(const GemmArgs& a, int slot) {
+  if (a.trace != nullptr) {
+    unsigned long long* t = a.trace + (static_cast<size_t>(blockIdx.x) * 8 + slot) * 2;
+    t[0] = static_cast<unsigned long long>(clock64());
+    t[1] = b2::globaltimer_ns();
+  }
+}
+
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
@@ -318,6 +327,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   b2::tc_fence_after();
   const uint32_t tmem_base = has_gemm ? *tmem_slot : 0;
   const unsigned int parity = (EPI == EPI_PUSH) ? (*seq_slot & 1u) : 0u;
+  if (threadIdx.x == 0) stamp(a, 0);
 
   if (has_gemm) {
     if (warp == 0) {
@@ -360,6 +370,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
           const uint32_t d_tmem = tmem_base + acc * BN;
           for (int kb = s.kb0; kb < s.kb1; ++kb) {
             if (!b2::mbar_wait(bar_full + stage * 8, phase, abort_flag, PIPE_LIMIT_NS, B2_WAIT_SMEM_FULL)) { ok = false; break; }
+            if (seg == 0 && kb == s.kb0) stamp(a, 1);
             b2::tc_fence_after();
             const uint32_t sp = smem_base + stage * C::STAGE_BYTES;
             const uint64_t dp = b2::umma_smem_desc(sp);
@@ -376,6 +387,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
           b2::umma_commit(bar_tfull + acc * 8);
           ++seg;
         }
+        stamp(a, 2);
       }
     } else {
       // ---------------- epilogue warps ----------------
@@ -386,6 +398,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
         const int acc = seg & 1;
         const uint32_t use = static_cast<uint32_t>(seg >> 1);
         if (!b2::mbar_wait(bar_tfull + acc * 8, use & 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_TMEM_FULL)) break;
+        if (warp == 2 && lane == 0 && u >= u_end) stamp(a, 3);  // the last segment's accumulator is complete
         b2::tc_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
         const int tp = s.tile / a.tilesQ, tq = s.tile - tp * a.tilesQ;
@@ -448,6 +461,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
         if (lane == 0) b2::mbar_arrive(bar_tempty + acc * 8);
         ++seg;
       }
+      if (warp == 2 && lane == 0) stamp(a, 4);
     }
   }
 
@@ -464,6 +478,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   }
   if (warp == 1 && has_gemm) b2::tmem_dealloc(tmem_base, C::TMEM_COLS);
 
+  if (threadIdx.x == 0) stamp(a, 5);
   if (EPI == EPI_PUSH) {
     if (!aborted) {
       switch (a.world) {
@@ -476,6 +491,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
     // the last CTA to finish advances the launch parity for the next call
     __syncthreads();
     if (threadIdx.x == 0) {
+      stamp(a, 6);
       __threadfence();
       const unsigned int prev = atomicAdd(&a.dstate->rowpar_done, 1u);
       if (prev == gridDim.x - 1) {
@@ -521,6 +537,7 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
   args.ws = ctx->splitk_ws;
   args.counters = ctx->tile_counters;
   args.status = ctx->status_dev;
+  args.trace = ctx->trace_on ? ctx->trace : nullptr;
   const int64_t tiles = static_cast<int64_t>(args.tilesP) * args.tilesQ;
   if (tiles > ctx->tile_counter_cap) return B2_ERR_SHAPE;
   const int64_t U = tiles * args.kblocks;
