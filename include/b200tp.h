@@ -105,6 +105,31 @@ int64_t b2_launch_count(void);
 int b2_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias,
             void* C, int64_t ldc, int M, int N, int K, void* stream);
 
+/* ---- the same GEMM for callers that cannot allocate device memory.  It has
+ *      no counterpart in the reference. ----------------------------------------
+ * b2_gemm needs a context, and creating one calls cudaMalloc.  Some users of
+ * this library never get that chance: a plug-in loaded after the serving
+ * engine has already handed every free byte of HBM to its KV cache (the
+ * reference sizes the cache from whatever is left, so a later cudaMalloc
+ * fails), or code that is only ever given a stream and tensors.  This variant
+ * takes no context: the kernel's scratch (the fp32 partials of output tiles
+ * whose K range is shared by several CTAs, and the tiles' arrival counters)
+ * is a fixed array compiled into the library, 9.3 MiB that every GPU using
+ * the library holds until the process ends.  Same arithmetic and result as
+ * b2_gemm, for decode-sized inputs only:
+ *   M <= 64 token rows and N <= 524288, otherwise B2_ERR_SHAPE (b2_last_error
+ *   says which limit was hit).
+ * The call allocates nothing, on the device or through any library.  The
+ * first call on each device looks up the array's address on that device
+ * (the device must be current); make that first call before any stream
+ * capture begins.  All calls share the one array: the counters are cleared on
+ * the stream at the start of every call, but two calls that overlap on the
+ * GPU (different streams, or different threads) race on it and corrupt each
+ * other's result - keep calls stream-ordered.  Without a context there is no
+ * status word: b2_status does not cover this entry point. */
+int b2_gemm_static_scratch(const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias,
+                           void* C, int64_t ldc, int M, int N, int K, void* stream);
+
 /* ---- row-parallel linear fused with its all-reduce, the residual add and
  *      the next RMSNorm: replaces RowParallelLinear.forward
  *      (nanovllm/layers/linear.py:152-156: F.linear then dist.all_reduce) AND

@@ -288,6 +288,7 @@ struct b2_ctx {
 
 namespace b2 {
 int set_cuda_error(cudaError_t e, const char* what);
+int set_error(int code, const char* fmt, ...);  // formats the text b2_last_error() returns; returns code
 void count_launch();
 int encode_tmap_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint64_t ld_elems,
                    uint32_t box_inner, uint32_t box_rows);

@@ -2,6 +2,7 @@
 // IPC, rank-local scratch, the host-visible status word, and the TMA
 // descriptor encoder.
 #include <atomic>
+#include <cstdarg>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -32,6 +33,13 @@ namespace b2 {
 int set_cuda_error(cudaError_t e, const char* what) {
   snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
   return B2_ERR_CUDA;
+}
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
 }
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 

@@ -23,6 +23,7 @@
 // results.  The inbox is data-as-flag: a slot holds the sentinel until the
 // value lands, and the reader puts the sentinel back after consuming it.
 #include <algorithm>
+#include <mutex>
 
 #include "b2_common.cuh"
 
@@ -719,3 +720,107 @@ int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int6
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// GEMM for callers that must not allocate: the split-tile workspace and the
+// arrival counters live in a file-scope device array instead of in a context.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr int STATIC_MAX_TOKENS = 64;    // largest M (token rows): the decode-sized tile, BN <= 64
+constexpr int STATIC_MAX_CTAS = 148;     // CTAs that may hold a split tile at once
+constexpr int STATIC_MAX_TILES = 4096;   // 128-row output tiles: N <= 524288
+constexpr size_t STATIC_COUNTER_BYTES = static_cast<size_t>(STATIC_MAX_TILES) * 4 * sizeof(int);
+constexpr size_t STATIC_WS_BYTES = static_cast<size_t>(STATIC_MAX_CTAS) * 2 * 128 * STATIC_MAX_TOKENS * sizeof(float);
+constexpr size_t STATIC_SCRATCH_BYTES = STATIC_COUNTER_BYTES + STATIC_WS_BYTES;  // 64 KiB + 9.25 MiB
+
+// Every GPU whose context loads this library carries these bytes until the
+// process exits.  Host code must never pass the symbol itself to a kernel: on
+// the host the name is only a handle; the device address comes from
+// cudaGetSymbolAddress, once per device, with that device current.
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+struct StaticScratch {
+  bool ready = false;
+  unsigned char* base = nullptr;
+  int num_sms = 0;
+};
+constexpr int STATIC_MAX_DEVICES = 64;
+StaticScratch g_static[STATIC_MAX_DEVICES];
+std::mutex g_static_mutex;
+
+int static_scratch_for_current_device(StaticScratch** out) {
+  int dev = -1;
+  B2_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= STATIC_MAX_DEVICES) return b2::set_error(B2_ERR_UNSUPPORTED, "b2_gemm_static_scratch: device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  StaticScratch& s = g_static[dev];
+  if (!s.ready) {
+    void* ptr = nullptr;
+    B2_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));  // the address on THIS device
+    if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 255) != 0)
+      return b2::set_error(B2_ERR_CUDA, "b2_gemm_static_scratch: bad device address %p for the static scratch", ptr);
+    int sms = 0;
+    B2_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    s.base = static_cast<unsigned char*>(ptr);
+    s.num_sms = sms;
+    s.ready = true;
+  }
+  *out = &s;
+  return B2_OK;
+}
+
+}  // namespace
+
+extern "C" int b2_gemm_static_scratch(const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias, void* C, int64_t ldc,
+                                      int M, int N, int K, void* stream) {
+  int rc = check_operands(A, lda, W, ldw, M, N, K);
+  if (rc != B2_OK) return rc;
+  if (M == 0) return B2_OK;
+  if (!C || !aligned16(C) || ldc % 8 != 0 || ldc < N) return B2_ERR_ARG;
+  if (bias != nullptr && !aligned16(bias)) return B2_ERR_ARG;
+  if (M > STATIC_MAX_TOKENS)
+    return b2::set_error(B2_ERR_SHAPE, "b2_gemm_static_scratch: M = %d exceeds the %d token rows the static scratch is sized for; use b2_gemm",
+                         M, STATIC_MAX_TOKENS);
+  const int tilesP = (N + BM - 1) / BM;
+  if (tilesP > STATIC_MAX_TILES)
+    return b2::set_error(B2_ERR_SHAPE, "b2_gemm_static_scratch: N = %d needs %d output tiles, the static scratch holds counters for %d; use b2_gemm",
+                         N, tilesP, STATIC_MAX_TILES);
+  StaticScratch* sc = nullptr;
+  rc = static_scratch_for_current_device(&sc);
+  if (rc != B2_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  const int bn = M <= 32 ? 32 : 64;
+  GemmArgs args{};
+  args.C = static_cast<uint16_t*>(C);
+  args.ldc = ldc;
+  args.bias = static_cast<const uint16_t*>(bias);
+  args.tilesP = tilesP;
+  args.tilesQ = 1;
+  args.kblocks = (K + BK - 1) / BK;
+  args.M = M;
+  args.N = N;
+  args.counters = reinterpret_cast<int*>(sc->base);
+  args.ws = reinterpret_cast<float*>(sc->base + STATIC_COUNTER_BYTES);
+  args.status = nullptr;  // no context, hence no status word: an expired pipeline wait only ends the kernel
+  args.trace = nullptr;
+  const int64_t U = static_cast<int64_t>(tilesP) * args.kblocks;
+  if (U > (1ll << 30)) return b2::set_error(B2_ERR_SHAPE, "b2_gemm_static_scratch: problem too large");
+  int64_t g = std::max<int64_t>(1, U / 8);
+  g = std::min<int64_t>(g, std::min(sc->num_sms, STATIC_MAX_CTAS));
+  g = std::min<int64_t>(g, U);
+  args.gemm_ctas = static_cast<int>(g);
+
+  // The array keeps whatever the previous call (or an aborted one) left behind.
+  // The counters must start at zero; the partials are always written before they are read.
+  B2_CUDA(cudaMemsetAsync(sc->base, 0, static_cast<size_t>(tilesP) * 4 * sizeof(int), s));
+
+  CUtensorMap tmP, tmQ;
+  rc = b2::encode_tmap_2d(&tmP, W, K, N, ldw, BK, BM);
+  if (rc != B2_OK) return rc;
+  rc = b2::encode_tmap_2d(&tmQ, A, K, M, lda, BK, bn);
+  if (rc != B2_OK) return rc;
+  if (bn == 32) return launch_inst<32, true, EPI_STORE>(tmP, tmQ, args, args.gemm_ctas, s);
+  return launch_inst<64, true, EPI_STORE>(tmP, tmQ, args, args.gemm_ctas, s);
+}
