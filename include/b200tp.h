@@ -81,8 +81,9 @@ int b2_status_clear(b2_ctx* ctx);
 /* Phase tracing of the GEMM / fused row-parallel kernel (the reference has
  * only per-step wall-clock in nanovllm/engine/llm_engine.py:72-83).  While
  * enabled, every CTA of those kernels records 8 (SM clock, global ns) stamps:
- * 0 start, 1 first operand tile landed, 2 last MMA issued, 3 last accumulator
- * complete, 4 epilogue done, 5 GEMM part left, 6 reduce phase done.  If
+ * 0 set-up done, 1 first operand tile landed, 2 last MMA issued, 3 earlier
+ * kernels complete (dependency wait passed), 4 epilogue done, 5 GEMM part
+ * left, 6 reduce phase done, 7 kernel entry.  If
  * host_out is non-NULL the call synchronises the device, copies
  * min(max_ctas, SM count) * 16 uint64 stamps of the most recent launch and
  * clears them.  Not for use during graph capture. */
@@ -101,7 +102,10 @@ int64_t b2_launch_count(void);
  * C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]), bf16 in, fp32 accumulate, bf16 out.
  * lda/ldw/ldc are row strides in elements (multiples of 8); K a multiple of 8.
  * tcgen05 tensor-core kernel fed by TMA; the work is split along K over the
- * SMs (stream-K) when there are fewer output tiles than SMs. */
+ * SMs (stream-K) when there are fewer output tiles than SMs.  W is treated as
+ * a constant: the kernel may start fetching it while the previous b2_* kernel
+ * on the stream is still running, so W must not be the output of a b2_* call
+ * that immediately precedes this one (A, bias and C have no such rule). */
 int b2_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias,
             void* C, int64_t ldc, int M, int N, int K, void* stream);
 

@@ -76,6 +76,15 @@ __device__ __forceinline__ void report_timeout(B2Status* st, int detail) {
   }
 }
 
+// ---- programmatic dependent launch -------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start
+// while the kernel before it in the stream is still running.  Everything it
+// does before pdl_wait() must be independent of earlier kernels (set-up,
+// loads of weights); pdl_wait() returns once every earlier kernel has
+// completed and its writes are visible.  Both are no-ops for a plain launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier --------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -290,6 +299,7 @@ namespace b2 {
 int set_cuda_error(cudaError_t e, const char* what);
 int set_error(int code, const char* fmt, ...);  // formats the text b2_last_error() returns; returns code
 void count_launch();
+bool pdl_enabled();  // false when the environment has B2_PDL=0
 int encode_tmap_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint64_t ld_elems,
                    uint32_t box_inner, uint32_t box_rows);
 }  // namespace b2
@@ -299,3 +309,22 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t 
     cudaError_t e__ = (call);                                    \
     if (e__ != cudaSuccess) return b2::set_cuda_error(e__, #call); \
   } while (0)
+
+// Launch with the programmatic-dependent-launch attribute (when enabled), so
+// that consecutive kernels of this library overlap set-up with the previous
+// kernel's tail.  Captured into CUDA graphs as a programmatic dependency.
+template <typename... KArgs, typename... Args>
+inline cudaError_t b2_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = b2::pdl_enabled() ? 1 : 0;
+  b2::count_launch();
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -4,6 +4,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -40,6 +41,13 @@ int set_error(int code, const char* fmt, ...) {
   vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
   va_end(ap);
   return code;
+}
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("B2_PDL");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
 }
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
@@ -124,8 +132,9 @@ int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
   c->peers_ready = (c->cfg.world == 1);
 
   // ---- rank-local scratch -----------------------------------------------------
-  c->splitk_ws_bytes = static_cast<size_t>(c->num_sms) * 2 * 128 * 256 * sizeof(float);
+  c->splitk_ws_bytes = static_cast<size_t>(c->num_sms) * 128 * 256 * sizeof(float);  // one 128 x 256 fp32 slot per CTA
   B2_CUDA(cudaMalloc(&c->splitk_ws, c->splitk_ws_bytes));
+  B2_CUDA(cudaMemset(c->splitk_ws, 0, c->splitk_ws_bytes));  // accumulation slots start (and are left) at zero
   c->tile_counter_cap = 1 << 16;
   B2_CUDA(cudaMalloc(&c->tile_counters, static_cast<size_t>(c->tile_counter_cap) * 4 * sizeof(int)));
   B2_CUDA(cudaMemset(c->tile_counters, 0, static_cast<size_t>(c->tile_counter_cap) * 4 * sizeof(int)));

@@ -38,6 +38,8 @@ __global__ void __launch_bounds__(256) store_kvcache_kernel(const uint16_t* __re
                                                             uint16_t* __restrict__ k_cache, uint16_t* __restrict__ v_cache,
                                                             const int32_t* __restrict__ slot_mapping, int n_tokens,
                                                             int vec_per_row) {
+  b2::pdl_launch_dependents();
+  b2::pdl_wait();
   const int64_t total = static_cast<int64_t>(n_tokens) * vec_per_row;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -63,6 +65,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* __restrict
                                                       const uint16_t* __restrict__ res, const uint16_t* __restrict__ w,
                                                       float eps, int rows, int dim, uint16_t* __restrict__ out, int64_t ldo,
                                                       uint16_t* __restrict__ res_out) {
+  b2::pdl_launch_dependents();
+  b2::pdl_wait();
   constexpr int VPT = 4;
   const int lanes = WARP_ROWS ? 32 : 256;
   const int lane = WARP_ROWS ? (threadIdx.x & 31) : threadIdx.x;
@@ -118,6 +122,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* __restrict
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) silu_mul_kernel(const uint16_t* __restrict__ x, int64_t ldx, int M, int I,
                                                        uint16_t* __restrict__ out) {
+  b2::pdl_launch_dependents();
+  b2::pdl_wait();
   const int vpr = I >> 3;
   const int64_t total = static_cast<int64_t>(M) * vpr;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -145,6 +151,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(uint16_t* __res
                                                                  float eps, const int64_t* __restrict__ positions,
                                                                  const float* __restrict__ cos_sin, uint16_t* __restrict__ k_cache,
                                                                  uint16_t* __restrict__ v_cache, const int32_t* __restrict__ slots) {
+  b2::pdl_launch_dependents();
+  b2::pdl_wait();
   constexpr int HD = 2 * HALF;
   constexpr int EPL = HALF / 32;  // elements per lane per half: 2 or 1
   const int heads = nq + 2 * nkv;
@@ -248,6 +256,8 @@ struct EmbedArgs {
 };
 
 __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
+  b2::pdl_launch_dependents();
+  b2::pdl_wait();
   const int vpr = a.H >> 3;
   const int64_t total = static_cast<int64_t>(a.M) * vpr;
   const int64_t first = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
@@ -317,6 +327,8 @@ __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
 // argmax over each row (first index wins ties)
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) argmax_kernel(const uint16_t* __restrict__ logits, int64_t ld, int V, int64_t* __restrict__ out) {
+  b2::pdl_launch_dependents();
+  b2::pdl_wait();
   const uint16_t* row = logits + blockIdx.x * ld;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
@@ -365,6 +377,8 @@ struct BcastArgs {
 };
 
 __global__ void __launch_bounds__(256) broadcast_tokens_kernel(const BcastArgs a) {
+  b2::pdl_launch_dependents();
+  b2::pdl_wait();
   const unsigned int parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->bcast_seq) & 1u;
   for (int i = threadIdx.x; i < a.n; i += blockDim.x) {
     if (a.rank == 0) {
@@ -399,6 +413,8 @@ __global__ void advance_decode_kernel(const int64_t* __restrict__ tokens, int64_
                                       int64_t* __restrict__ positions, int32_t* __restrict__ context_lens,
                                       int32_t* __restrict__ slot_mapping, const int32_t* __restrict__ block_tables,
                                       int64_t bt_stride, int block_size, int n) {
+  b2::pdl_launch_dependents();
+  b2::pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   input_ids[i] = tokens[i];
@@ -430,11 +446,9 @@ int b2_store_kvcache(const void* key, int64_t key_stride, const void* value, int
   if (key_stride % 8 != 0 || value_stride % 8 != 0 || key_stride < D || value_stride < D) return B2_ERR_ARG;
   const int vpr = D / 8;
   const int grid = grid_for(static_cast<int64_t>(n_tokens) * vpr, 256, 148 * 16);
-  store_kvcache_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint16_t*>(key), key_stride, static_cast<const uint16_t*>(value), value_stride,
-      static_cast<uint16_t*>(k_cache), static_cast<uint16_t*>(v_cache), slot_mapping, n_tokens, vpr);
-  b2::count_launch();
-  B2_CUDA(cudaGetLastError());
+  B2_CUDA(b2_launch(store_kvcache_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const uint16_t*>(key), key_stride, static_cast<const uint16_t*>(value), value_stride,
+                    static_cast<uint16_t*>(k_cache), static_cast<uint16_t*>(v_cache), slot_mapping, n_tokens, vpr));
   return B2_OK;
 }
 
@@ -453,14 +467,12 @@ static int launch_rmsnorm(bool add, const void* x, int64_t ldx, const void* res,
   uint16_t* ro = static_cast<uint16_t*>(res_out);
   if (dim <= 1024) {
     const int grid = (rows + 7) / 8;
-    if (add) rmsnorm_kernel<true, true><<<grid, 256, 0, s>>>(xx, ldx, rr, ww, eps, rows, dim, oo, ldo, ro);
-    else rmsnorm_kernel<false, true><<<grid, 256, 0, s>>>(xx, ldx, rr, ww, eps, rows, dim, oo, ldo, ro);
+    if (add) B2_CUDA(b2_launch(rmsnorm_kernel<true, true>, dim3(grid), dim3(256), 0, s, xx, ldx, rr, ww, eps, rows, dim, oo, ldo, ro));
+    else B2_CUDA(b2_launch(rmsnorm_kernel<false, true>, dim3(grid), dim3(256), 0, s, xx, ldx, rr, ww, eps, rows, dim, oo, ldo, ro));
   } else {
-    if (add) rmsnorm_kernel<true, false><<<rows, 256, 0, s>>>(xx, ldx, rr, ww, eps, rows, dim, oo, ldo, ro);
-    else rmsnorm_kernel<false, false><<<rows, 256, 0, s>>>(xx, ldx, rr, ww, eps, rows, dim, oo, ldo, ro);
+    if (add) B2_CUDA(b2_launch(rmsnorm_kernel<true, false>, dim3(rows), dim3(256), 0, s, xx, ldx, rr, ww, eps, rows, dim, oo, ldo, ro));
+    else B2_CUDA(b2_launch(rmsnorm_kernel<false, false>, dim3(rows), dim3(256), 0, s, xx, ldx, rr, ww, eps, rows, dim, oo, ldo, ro));
   }
-  b2::count_launch();
-  B2_CUDA(cudaGetLastError());
   return B2_OK;
 }
 
@@ -478,10 +490,8 @@ int b2_silu_and_mul(const void* x, int64_t ldx, int M, int I, void* out, void* s
   if (M == 0) return B2_OK;
   if (!x || !out || !aligned16(x) || !aligned16(out)) return B2_ERR_ARG;
   const int grid = grid_for(static_cast<int64_t>(M) * (I / 8), 256, 148 * 16);
-  silu_mul_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint16_t*>(x), ldx, M, I,
-                                                                       static_cast<uint16_t*>(out));
-  b2::count_launch();
-  B2_CUDA(cudaGetLastError());
+  B2_CUDA(b2_launch(silu_mul_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(x), ldx, M, I,
+                    static_cast<uint16_t*>(out)));
   return B2_OK;
 }
 
@@ -496,18 +506,15 @@ int b2_qk_norm_rope_store(void* qkv, int64_t ld_qkv, int M, int nq, int nkv, int
   const int64_t warps = static_cast<int64_t>(M) * (nq + 2 * nkv);
   const int grid = static_cast<int>((warps + 7) / 8);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint16_t* qp = static_cast<uint16_t*>(qkv);
+  const uint16_t* qw = static_cast<const uint16_t*>(q_norm_w);
+  const uint16_t* kw = static_cast<const uint16_t*>(k_norm_w);
+  uint16_t* kc = static_cast<uint16_t*>(k_cache);
+  uint16_t* vc = static_cast<uint16_t*>(v_cache);
   if (head_dim == 128)
-    qk_norm_rope_store_kernel<64><<<grid, 256, 0, s>>>(static_cast<uint16_t*>(qkv), ld_qkv, M, nq, nkv,
-                                                       static_cast<const uint16_t*>(q_norm_w), static_cast<const uint16_t*>(k_norm_w), eps,
-                                                       positions, cos_sin, static_cast<uint16_t*>(k_cache),
-                                                       static_cast<uint16_t*>(v_cache), slot_mapping);
+    B2_CUDA(b2_launch(qk_norm_rope_store_kernel<64>, dim3(grid), dim3(256), 0, s, qp, ld_qkv, M, nq, nkv, qw, kw, eps, positions, cos_sin, kc, vc, slot_mapping));
   else
-    qk_norm_rope_store_kernel<32><<<grid, 256, 0, s>>>(static_cast<uint16_t*>(qkv), ld_qkv, M, nq, nkv,
-                                                       static_cast<const uint16_t*>(q_norm_w), static_cast<const uint16_t*>(k_norm_w), eps,
-                                                       positions, cos_sin, static_cast<uint16_t*>(k_cache),
-                                                       static_cast<uint16_t*>(v_cache), slot_mapping);
-  b2::count_launch();
-  B2_CUDA(cudaGetLastError());
+    B2_CUDA(b2_launch(qk_norm_rope_store_kernel<32>, dim3(grid), dim3(256), 0, s, qp, ld_qkv, M, nq, nkv, qw, kw, eps, positions, cos_sin, kc, vc, slot_mapping));
   return B2_OK;
 }
 
@@ -533,9 +540,7 @@ int b2_embed(b2_ctx* ctx, const int64_t* ids, const void* W, int64_t vocab_start
   }
   const int cap = ctx ? ctx->num_sms * 4 : 148 * 4;
   const int grid = grid_for(static_cast<int64_t>(M) * (H / 8), 256, cap);
-  embed_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
-  b2::count_launch();
-  B2_CUDA(cudaGetLastError());
+  B2_CUDA(b2_launch(embed_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), a));
   return B2_OK;
 }
 
@@ -552,9 +557,7 @@ int b2_broadcast_tokens(b2_ctx* ctx, int64_t* buf, int n, void* stream) {
   a.dstate = ctx->dstate;
   a.status = ctx->status_dev;
   a.timeout_ns = static_cast<uint64_t>(ctx->cfg.timeout_ms) * 1000000ull;
-  broadcast_tokens_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
-  b2::count_launch();
-  B2_CUDA(cudaGetLastError());
+  B2_CUDA(b2_launch(broadcast_tokens_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), a));
   return B2_OK;
 }
 
@@ -563,10 +566,8 @@ int b2_advance_decode(const int64_t* tokens, int64_t* input_ids, int64_t* positi
   if (n < 0 || block_size <= 0) return B2_ERR_ARG;
   if (n == 0) return B2_OK;
   if (!tokens || !input_ids || !positions || !context_lens || !slot_mapping || !block_tables) return B2_ERR_ARG;
-  advance_decode_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(tokens, input_ids, positions, context_lens,
-                                                                                       slot_mapping, block_tables, bt_stride, block_size, n);
-  b2::count_launch();
-  B2_CUDA(cudaGetLastError());
+  B2_CUDA(b2_launch(advance_decode_kernel, dim3((n + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream), tokens, input_ids, positions,
+                    context_lens, slot_mapping, block_tables, bt_stride, block_size, n));
   return B2_OK;
 }
 
@@ -574,9 +575,7 @@ int b2_argmax(const void* logits, int64_t ld, int B, int V, int64_t* out, void* 
   if (B < 0 || V <= 0 || ld % 8 != 0 || ld < V) return B2_ERR_ARG;
   if (B == 0) return B2_OK;
   if (!logits || !out || !aligned16(logits)) return B2_ERR_ARG;
-  argmax_kernel<<<B, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint16_t*>(logits), ld, V, out);
-  b2::count_launch();
-  B2_CUDA(cudaGetLastError());
+  B2_CUDA(b2_launch(argmax_kernel, dim3(B), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(logits), ld, V, out));
   return B2_OK;
 }
 

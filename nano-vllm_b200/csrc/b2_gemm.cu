@@ -12,9 +12,9 @@
 //
 // Work unit = one 64-wide K block of one output tile.  The units are dealt in
 // contiguous ranges to the CTAs; a tile whose K range is shared by several
-// CTAs is combined through fp32 partials in a workspace: the CTA that arrives
-// last at the tile's counter adds the others' partials to its own accumulator
-// and writes the output.  Nobody waits for anybody.
+// CTAs is combined in an fp32 accumulation slot in L2 (vector red.add): the
+// CTA that arrives last at the tile's counter reads the sum, re-zeroes the
+// slot and writes the output.  Nobody waits for anybody.
 //
 // EPI_PUSH: the fused row-parallel path.  The epilogue rounds the tile to bf16
 // and stores it into the inbox of every rank (its own and, over NVLink, its
@@ -169,73 +169,105 @@ __device__ __forceinline__ void emit_chunk(const GemmArgs& a, float (&v)[32], in
 
 // ---------------------------------------------------------------------------
 // Reduce phase of the fused row-parallel call: one CTA per token row.
-// S = number of source ranks.
+// S = number of source ranks.  The loads of a row (residual, every source's
+// partial, norm weight) are issued together, G vectors at a time, so that a
+// thread pays one memory round trip per group instead of one per vector.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ void add8(float (&acc)[8], const uint4& v) {
+  acc[0] += b2::bf16_lo(v.x); acc[1] += b2::bf16_hi(v.x); acc[2] += b2::bf16_lo(v.y); acc[3] += b2::bf16_hi(v.y);
+  acc[4] += b2::bf16_lo(v.z); acc[5] += b2::bf16_hi(v.z); acc[6] += b2::bf16_lo(v.w); acc[7] += b2::bf16_hi(v.w);
+}
+__device__ __forceinline__ uint4 pack8f(const float (&f)[8]) {
+  return make_uint4(b2::pack_bf16(f[0], f[1]), b2::pack_bf16(f[2], f[3]), b2::pack_bf16(f[4], f[5]), b2::pack_bf16(f[6], f[7]));
+}
+
 template <int S>
 __device__ __forceinline__ void reduce_rows(const GemmArgs& a, unsigned int parity, float* red, volatile int* gave_up) {
+  constexpr int G = S >= 8 ? 2 : (S == 4 ? 3 : MAX_ROW_VECS);  // vectors in flight together: G * S <= 16 loads of 16 bytes
   const int nvec = a.N >> 3;
   const int tid = threadIdx.x;
+  const bool with_norm = a.norm_w != nullptr;
   unsigned char* my = a.inbox[a.rank] + parity * a.parity_stride;
   const uint4 sentinel = make_uint4(B2_SENTINEL32, B2_SENTINEL32, B2_SENTINEL32, B2_SENTINEL32);
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
   for (int row = blockIdx.x; row < a.M; row += gridDim.x) {
     float acc[MAX_ROW_VECS][8];
     float ss = 0.f;
+    const size_t row_off = static_cast<size_t>(row) * a.N;
 #pragma unroll
-    for (int it = 0; it < MAX_ROW_VECS; ++it) {
-      const int v = tid + it * NUM_THREADS;
-      if (v < nvec) {
-        const size_t off = (static_cast<size_t>(row) * a.N + v * 8) * 2;
-        uint4 val[S];
-        bool pending = true;
-        uint64_t t0 = 0;
-        for (uint32_t spin = 0; pending; ++spin) {
-          pending = false;
+    for (int g0 = 0; g0 < MAX_ROW_VECS; g0 += G) {
+      if (tid + g0 * NUM_THREADS >= nvec) break;
+      uint4 resv[G];
+      uint4 val[G][S];
+      // residual first: it does not depend on the partials
 #pragma unroll
-          for (int s = 0; s < S; ++s) val[s] = b2::ld_volatile_v4(my + s * a.slot_stride + off);
+      for (int i = 0; i < G; ++i) {
+        const int v = tid + (g0 + i) * NUM_THREADS;
+        resv[i] = (with_norm && v < nvec) ? __ldg(reinterpret_cast<const uint4*>(a.residual_in + row_off + v * 8)) : zero4;
+      }
+      bool pending = true;
+      uint64_t t0 = 0;
+      for (uint32_t spin = 0; pending; ++spin) {
+        pending = false;
 #pragma unroll
-          for (int s = 0; s < S; ++s) pending |= b2::has_sentinel(val[s]);
-          if (pending && (spin & 0x3F) == 0x3F) {
-            // one expired wait ends every later wait of this CTA at once
-            if (*gave_up) break;
-            const uint64_t now = b2::globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > a.timeout_ns) {
-              *gave_up = 1;
-              b2::report_timeout(a.status, B2_WAIT_PARTIALS);
-              break;
-            }
+        for (int i = 0; i < G; ++i) {
+          const int v = tid + (g0 + i) * NUM_THREADS;
+          if (v < nvec) {
+#pragma unroll
+            for (int s = 0; s < S; ++s) val[i][s] = b2::ld_volatile_v4(my + s * a.slot_stride + (row_off + v * 8) * 2);
           }
         }
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[it][e] = 0.f;
+        for (int i = 0; i < G; ++i) {
+          const int v = tid + (g0 + i) * NUM_THREADS;
+          if (v < nvec) {
 #pragma unroll
-        for (int s = 0; s < S; ++s) {
-          acc[it][0] += b2::bf16_lo(val[s].x); acc[it][1] += b2::bf16_hi(val[s].x);
-          acc[it][2] += b2::bf16_lo(val[s].y); acc[it][3] += b2::bf16_hi(val[s].y);
-          acc[it][4] += b2::bf16_lo(val[s].z); acc[it][5] += b2::bf16_hi(val[s].z);
-          acc[it][6] += b2::bf16_lo(val[s].w); acc[it][7] += b2::bf16_hi(val[s].w);
-          *reinterpret_cast<uint4*>(my + s * a.slot_stride + off) = sentinel;  // consumed
+            for (int s = 0; s < S; ++s) pending |= b2::has_sentinel(val[i][s]);
+          }
         }
-        const size_t eoff = static_cast<size_t>(row) * a.N + v * 8;
-        if (a.norm_w != nullptr) {
-          const uint4 rv = *reinterpret_cast<const uint4*>(a.residual_in + eoff);
-          acc[it][0] += b2::bf16_lo(rv.x); acc[it][1] += b2::bf16_hi(rv.x);
-          acc[it][2] += b2::bf16_lo(rv.y); acc[it][3] += b2::bf16_hi(rv.y);
-          acc[it][4] += b2::bf16_lo(rv.z); acc[it][5] += b2::bf16_hi(rv.z);
-          acc[it][6] += b2::bf16_lo(rv.w); acc[it][7] += b2::bf16_hi(rv.w);
-          *reinterpret_cast<uint4*>(a.residual_out + eoff) =
-              make_uint4(b2::pack_bf16(acc[it][0], acc[it][1]), b2::pack_bf16(acc[it][2], acc[it][3]),
-                         b2::pack_bf16(acc[it][4], acc[it][5]), b2::pack_bf16(acc[it][6], acc[it][7]));
+        if (pending && (spin & 0x3F) == 0x3F) {
+          // one expired wait ends every later wait of this CTA at once
+          if (*gave_up) break;
+          const uint64_t now = b2::globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > a.timeout_ns) {
+            *gave_up = 1;
+            b2::report_timeout(a.status, B2_WAIT_PARTIALS);
+            break;
+          }
+        }
+      }
 #pragma unroll
-          for (int e = 0; e < 8; ++e) ss += acc[it][e] * acc[it][e];
-        } else {
-          *reinterpret_cast<uint4*>(a.normed_out + eoff) =
-              make_uint4(b2::pack_bf16(acc[it][0], acc[it][1]), b2::pack_bf16(acc[it][2], acc[it][3]),
-                         b2::pack_bf16(acc[it][4], acc[it][5]), b2::pack_bf16(acc[it][6], acc[it][7]));
+      for (int i = 0; i < G; ++i) {
+        const int v = tid + (g0 + i) * NUM_THREADS;
+        if (v < nvec) {
+          const size_t eoff = row_off + v * 8;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[g0 + i][e] = 0.f;
+#pragma unroll
+          for (int s = 0; s < S; ++s) {
+            add8(acc[g0 + i], val[i][s]);
+            *reinterpret_cast<uint4*>(my + s * a.slot_stride + eoff * 2) = sentinel;  // consumed
+          }
+          if (with_norm) {
+            add8(acc[g0 + i], resv[i]);
+            *reinterpret_cast<uint4*>(a.residual_out + eoff) = pack8f(acc[g0 + i]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += acc[g0 + i][e] * acc[g0 + i][e];
+          } else {
+            *reinterpret_cast<uint4*>(a.normed_out + eoff) = pack8f(acc[g0 + i]);
+          }
         }
       }
     }
-    if (a.norm_w == nullptr) continue;  // plain all-reduce: done with this row (uniform across the CTA)
+    if (!with_norm) continue;  // plain all-reduce: done with this row (uniform across the CTA)
+    // the norm weights travel while the row's sum of squares is being combined
+    uint4 wv[MAX_ROW_VECS];
+#pragma unroll
+    for (int it = 0; it < MAX_ROW_VECS; ++it) {
+      const int v = tid + it * NUM_THREADS;
+      wv[it] = v < nvec ? __ldg(reinterpret_cast<const uint4*>(a.norm_w + v * 8)) : zero4;
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     __syncthreads();  // red[] free again
@@ -249,14 +281,12 @@ __device__ __forceinline__ void reduce_rows(const GemmArgs& a, unsigned int pari
     for (int it = 0; it < MAX_ROW_VECS; ++it) {
       const int v = tid + it * NUM_THREADS;
       if (v < nvec) {
-        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(a.norm_w + v * 8));
         float o[8];
-        o[0] = b2::bf16_round(acc[it][0] * rstd) * b2::bf16_lo(wv.x); o[1] = b2::bf16_round(acc[it][1] * rstd) * b2::bf16_hi(wv.x);
-        o[2] = b2::bf16_round(acc[it][2] * rstd) * b2::bf16_lo(wv.y); o[3] = b2::bf16_round(acc[it][3] * rstd) * b2::bf16_hi(wv.y);
-        o[4] = b2::bf16_round(acc[it][4] * rstd) * b2::bf16_lo(wv.z); o[5] = b2::bf16_round(acc[it][5] * rstd) * b2::bf16_hi(wv.z);
-        o[6] = b2::bf16_round(acc[it][6] * rstd) * b2::bf16_lo(wv.w); o[7] = b2::bf16_round(acc[it][7] * rstd) * b2::bf16_hi(wv.w);
-        *reinterpret_cast<uint4*>(a.normed_out + static_cast<size_t>(row) * a.N + v * 8) =
-            make_uint4(b2::pack_bf16(o[0], o[1]), b2::pack_bf16(o[2], o[3]), b2::pack_bf16(o[4], o[5]), b2::pack_bf16(o[6], o[7]));
+        o[0] = b2::bf16_round(acc[it][0] * rstd) * b2::bf16_lo(wv[it].x); o[1] = b2::bf16_round(acc[it][1] * rstd) * b2::bf16_hi(wv[it].x);
+        o[2] = b2::bf16_round(acc[it][2] * rstd) * b2::bf16_lo(wv[it].y); o[3] = b2::bf16_round(acc[it][3] * rstd) * b2::bf16_hi(wv[it].y);
+        o[4] = b2::bf16_round(acc[it][4] * rstd) * b2::bf16_lo(wv[it].z); o[5] = b2::bf16_round(acc[it][5] * rstd) * b2::bf16_hi(wv[it].z);
+        o[6] = b2::bf16_round(acc[it][6] * rstd) * b2::bf16_lo(wv[it].w); o[7] = b2::bf16_round(acc[it][7] * rstd) * b2::bf16_hi(wv[it].w);
+        *reinterpret_cast<uint4*>(a.normed_out + row_off + v * 8) = pack8f(o);
       }
     }
   }
@@ -289,7 +319,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   const uint32_t bar_tempty = bar_tfull + 2 * 8;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile unsigned int* seq_slot = reinterpret_cast<volatile unsigned int*>(tmem_slot + 2);
   __shared__ float red[NUM_THREADS / 32];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -305,6 +334,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   const int u_end = has_gemm ? part.u0(cta + 1) : 0;
 
   if (threadIdx.x == 0) {
+    stamp(a, 7);
     b2::tma_prefetch_desc(&tmP);
     b2::tma_prefetch_desc(&tmQ);
     for (int s = 0; s < STAGES; ++s) {
@@ -316,7 +346,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
       b2::mbar_init(bar_tempty + i * 8, 4);
     }
     *abort_flag = 0;
-    if (EPI == EPI_PUSH) *seq_slot = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq);
     b2::mbar_fence_init();
   }
   if (warp == 1 && has_gemm) {
@@ -327,8 +356,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   __syncthreads();
   b2::tc_fence_after();
   const uint32_t tmem_base = has_gemm ? *tmem_slot : 0;
-  const unsigned int parity = (EPI == EPI_PUSH) ? (*seq_slot & 1u) : 0u;
+  // the next kernel in the stream may start its own set-up from now on
+  if (threadIdx.x == 0) b2::pdl_launch_dependents();
   if (threadIdx.x == 0) stamp(a, 0);
+  unsigned int parity = 0;
 
   if (has_gemm) {
     if (warp == 0) {
@@ -336,22 +367,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
       if (lane == 0) {
         const uint64_t polP = SWAP ? b2::kEvictFirst : b2::kEvictNormal;
         const uint64_t polQ = SWAP ? b2::kEvictLast : b2::kEvictNormal;
-        int stage = 0;
-        uint32_t phase = 0;
-        int u = u_begin;
-        Seg s;
-        bool ok = true;
-        while (ok && next_seg(u, u_end, KB, s)) {
-          const int tp = s.tile / a.tilesQ, tq = s.tile - tp * a.tilesQ;
-          for (int kb = s.kb0; kb < s.kb1; ++kb) {
-            if (!b2::mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_SMEM_EMPTY)) { ok = false; break; }
-            const uint32_t fb = bar_full + stage * 8;
-            b2::mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
-            const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
-            b2::tma_load_2d(dst, &tmP, fb, kb * BK, tp * BM, polP);
-            b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, kb * BK, tq * BN, polQ);
-            if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          }
+        const int n_units = u_end - u_begin;
+        const int pre = n_units < STAGES ? n_units : STAGES;
+        // The weight tiles of the first stages depend on no earlier kernel: fetch them before the
+        // dependency wait, so that they are in flight (or landed) when the activations become valid.
+        for (int i = 0; i < pre; ++i) {
+          const int u = u_begin + i, tile = u / KB, kb = u - tile * KB;
+          const int tp = tile / a.tilesQ, tq = tile - tp * a.tilesQ;
+          const uint32_t fb = bar_full + i * 8;
+          b2::mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
+          const uint32_t dst = smem_base + i * C::STAGE_BYTES;
+          if (SWAP) b2::tma_load_2d(dst, &tmP, fb, kb * BK, tp * BM, polP);
+          else b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, kb * BK, tq * BN, polQ);
+        }
+        b2::pdl_wait();
+        stamp(a, 3);
+        for (int i = 0; i < pre; ++i) {
+          const int u = u_begin + i, tile = u / KB, kb = u - tile * KB;
+          const int tp = tile / a.tilesQ, tq = tile - tp * a.tilesQ;
+          const uint32_t fb = bar_full + i * 8;
+          const uint32_t dst = smem_base + i * C::STAGE_BYTES;
+          if (SWAP) b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, kb * BK, tq * BN, polQ);
+          else b2::tma_load_2d(dst, &tmP, fb, kb * BK, tp * BM, polP);
+        }
+        int stage = pre == STAGES ? 0 : pre;
+        uint32_t phase = pre == STAGES ? 1 : 0;
+        for (int i = pre; i < n_units; ++i) {
+          const int u = u_begin + i, tile = u / KB, kb = u - tile * KB;
+          const int tp = tile / a.tilesQ, tq = tile - tp * a.tilesQ;
+          if (!b2::mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_SMEM_EMPTY)) break;
+          const uint32_t fb = bar_full + stage * 8;
+          b2::mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
+          const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
+          b2::tma_load_2d(dst, &tmP, fb, kb * BK, tp * BM, polP);
+          b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, kb * BK, tq * BN, polQ);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     } else if (warp == 1) {
@@ -393,13 +443,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
     } else {
       // ---------------- epilogue warps ----------------
       const int q = warp & 3;  // TMEM lane quadrant this warp may read
+      b2::pdl_wait();
+      if (EPI == EPI_PUSH) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
       int u = u_begin, seg = 0;
       Seg s;
       while (next_seg(u, u_end, KB, s)) {
         const int acc = seg & 1;
         const uint32_t use = static_cast<uint32_t>(seg >> 1);
         if (!b2::mbar_wait(bar_tfull + acc * 8, use & 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_TMEM_FULL)) break;
-        if (warp == 2 && lane == 0 && u >= u_end) stamp(a, 3);  // the last segment's accumulator is complete
         b2::tc_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
         const int tp = s.tile / a.tilesQ, tq = s.tile - tp * a.tilesQ;
@@ -417,42 +468,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
             emit_chunk<SWAP, EPI>(a, v, p_row, tq * BN + c * 32, lane, parity);
           }
         } else {
-          // this CTA holds only part of the tile's K range
-          const int my_slot = (seg == 0) ? 0 : 1;
-          float* mine = a.ws + ((static_cast<size_t>(cta) * 2 + my_slot) * 4 + q) * (BN * 32);
+          // This CTA holds only part of the tile's K range.  Every contributor adds its part into the
+          // tile's fp32 accumulation slot (vector reductions that complete in L2; nobody waits for them);
+          // the contributor that arrives last at the tile's counter reads the sum once, puts the slot
+          // back to zero for the next launch, and writes the output.  The slot of a split tile is indexed
+          // by its first contributor, which is unique among split tiles.
+          const int c_first = part.cta_of(s.tile * KB), c_last = part.cta_of(s.tile * KB + KB - 1);
+          float* slot = a.ws + (static_cast<size_t>(c_first) * 4 + q) * (BN * 32) + lane * 4;
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             uint32_t r[32];
             b2::tmem_ld_32x32(taddr + c * 32, r);
             b2::tc_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) mine[(c * 32 + j) * 32 + lane] = __uint_as_float(r[j]);
+            for (int j = 0; j < 8; ++j)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(slot + (c * 8 + j) * 128), "f"(__uint_as_float(r[4 * j])),
+                           "f"(__uint_as_float(r[4 * j + 1])), "f"(__uint_as_float(r[4 * j + 2])), "f"(__uint_as_float(r[4 * j + 3]))
+                           : "memory");
           }
           __threadfence();
           __syncwarp();
-          const int c_first = part.cta_of(s.tile * KB), c_last = part.cta_of(s.tile * KB + KB - 1);
           int old = 0;
           if (lane == 0) old = atomicAdd(a.counters + s.tile * 4 + q, 1);
           old = __shfl_sync(0xffffffffu, old, 0);
           if (old == c_last - c_first) {
-            // last to arrive: every other contributor's partial is complete
             __threadfence();
             if (lane == 0) a.counters[s.tile * 4 + q] = 0;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
-              uint32_t r[32];
-              b2::tmem_ld_32x32(taddr + c * 32, r);
-              b2::tc_wait_ld();
               float v[32];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-              for (int cc = c_first; cc <= c_last; ++cc) {
-                if (cc == cta) continue;
-                const int slot = (part.u0(cc) / KB == s.tile) ? 0 : 1;
-                const float* other = a.ws + ((static_cast<size_t>(cc) * 2 + slot) * 4 + q) * (BN * 32) + c * 32 * 32 + lane;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] += b2::ld_cg_f32(other + j * 32);
+              for (int j = 0; j < 8; ++j) {
+                float4 t;
+                asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(t.x), "=f"(t.y), "=f"(t.z), "=f"(t.w) : "l"(slot + (c * 8 + j) * 128) : "memory");
+                v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
               }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(slot + (c * 8 + j) * 128) = make_float4(0.f, 0.f, 0.f, 0.f);
               emit_chunk<SWAP, EPI>(a, v, p_row, tq * BN + c * 32, lane, parity);
             }
           }
@@ -467,6 +519,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   }
 
   // ---- all roles meet; tensor memory goes back ------------------------------
+  b2::pdl_wait();
+  if (EPI == EPI_PUSH) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
   __syncwarp();
   b2::tc_fence_before();
   __syncthreads();
@@ -516,9 +570,7 @@ int launch_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmArgs& 
     B2_CUDA(cudaFuncSetAttribute(gemm_kernel<BN, SWAP, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
     configured = true;
   }
-  gemm_kernel<BN, SWAP, EPI><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(tmP, tmQ, args);
-  b2::count_launch();
-  B2_CUDA(cudaGetLastError());
+  B2_CUDA(b2_launch(gemm_kernel<BN, SWAP, EPI>, dim3(grid), dim3(NUM_THREADS), Cfg<BN>::SMEM_BYTES, stream, tmP, tmQ, args));
   return B2_OK;
 }
 
@@ -586,6 +638,8 @@ int check_operands(const void* A, int64_t lda, const void* W, int64_t ldw, int M
 __global__ void __launch_bounds__(256) gather_rows_kernel(const uint16_t* __restrict__ h, int64_t ldh,
                                                           const int32_t* __restrict__ idx, int B, int H,
                                                           uint16_t* __restrict__ out) {
+  b2::pdl_launch_dependents();
+  b2::pdl_wait();
   const int vpr = H >> 3;
   const int64_t total = static_cast<int64_t>(B) * vpr;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -603,6 +657,7 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint16_t* __rest
 __global__ void lm_head_sync_kernel(int rank, int world, unsigned int* flags_rank0, B2DeviceState* dstate, B2Status* status,
                                     uint64_t timeout_ns) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  b2::pdl_wait();
   const unsigned int want = dstate->lmhead_seq + 1;
   if (rank != 0) {
     __threadfence_system();
@@ -645,10 +700,8 @@ int b2_lm_head(b2_ctx* ctx, const void* h, int64_t ldh, const int32_t* row_index
   if (row_index != nullptr) {
     const int64_t work = static_cast<int64_t>(B) * (H / 8);
     const int grid = static_cast<int>(std::min<int64_t>((work + 255) / 256, ctx->num_sms * 4));
-    gather_rows_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(h), ldh, row_index, B, H,
-                                            reinterpret_cast<uint16_t*>(ctx->gather_rows));
-    b2::count_launch();
-    B2_CUDA(cudaGetLastError());
+    B2_CUDA(b2_launch(gather_rows_kernel, dim3(grid), dim3(256), 0, s, static_cast<const uint16_t*>(h), ldh, row_index, B, H,
+                      reinterpret_cast<uint16_t*>(ctx->gather_rows)));
     A = ctx->gather_rows;
     lda = H;
   }
@@ -658,10 +711,8 @@ int b2_lm_head(b2_ctx* ctx, const void* h, int64_t ldh, const int32_t* row_index
   rc = launch_gemm<EPI_STORE>(ctx, A, lda, W, ldw, B, Vr, H, args, 0, s);
   if (rc != B2_OK) return rc;
   if (world > 1) {
-    lm_head_sync_kernel<<<1, 32, 0, s>>>(rank, world, reinterpret_cast<unsigned int*>(ctx->peer[0] + ctx->off_flags), ctx->dstate,
-                                         ctx->status_dev, static_cast<uint64_t>(ctx->cfg.timeout_ms) * 1000000ull);
-    b2::count_launch();
-    B2_CUDA(cudaGetLastError());
+    B2_CUDA(b2_launch(lm_head_sync_kernel, dim3(1), dim3(32), 0, s, rank, world, reinterpret_cast<unsigned int*>(ctx->peer[0] + ctx->off_flags),
+                      ctx->dstate, ctx->status_dev, static_cast<uint64_t>(ctx->cfg.timeout_ms) * 1000000ull));
   }
   if (rank == 0) *logits_out = ctx->symm + ctx->off_logits;
   return B2_OK;
@@ -813,8 +864,9 @@ extern "C" int b2_gemm_static_scratch(const void* A, int64_t lda, const void* W,
   args.gemm_ctas = static_cast<int>(g);
 
   // The array keeps whatever the previous call (or an aborted one) left behind.
-  // The counters must start at zero; the partials are always written before they are read.
+  // The counters and the accumulation slots of split tiles must start at zero.
   B2_CUDA(cudaMemsetAsync(sc->base, 0, static_cast<size_t>(tilesP) * 4 * sizeof(int), s));
+  B2_CUDA(cudaMemsetAsync(sc->base + STATIC_COUNTER_BYTES, 0, static_cast<size_t>(args.gemm_ctas) * 128 * bn * sizeof(float), s));
 
   CUtensorMap tmP, tmQ;
   rc = b2::encode_tmap_2d(&tmP, W, K, N, ldw, BK, BM);

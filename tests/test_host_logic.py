@@ -69,6 +69,9 @@ def test_streamk_partition_covers_every_unit_once(tiles, kb):
         first, last = p.cta_of(tile * kb), p.cta_of(tile * kb + kb - 1)
         who = sorted({c for c in range(g) for (t, _, _) in segments(p, c, kb) if t == tile})
         assert who == list(range(first, last + 1))
+    # a split tile accumulates in the slot of its first contributor: no two split tiles share one
+    owners = [p.cta_of(t * kb) for t in range(tiles) if p.cta_of(t * kb) != p.cta_of(t * kb + kb - 1)]
+    assert len(owners) == len(set(owners))
 
 
 # ---- weight loaders ------------------------------------------------------------
