@@ -154,6 +154,26 @@ int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int6
                     int M, int N, int Kr, const void* residual_in, const void* norm_w, float eps,
                     void* normed_out, void* residual_out, void* stream);
 
+/* The same block in its two-shot form, for many tokens (M above a few hundred)
+ * at tensor-parallel size >= 2.  Token rows are dealt to the ranks in blocks
+ * of 128 rows, round-robin (rank r owns rows [128 b, 128 b + 128) for
+ * b = r, r + world, ...).  Each rank's GEMM epilogue sends
+ * a partial row only to the rank that owns it; the owner reduces, adds the
+ * residual, normalises and stores the finished row into every rank's output
+ * buffer.  NVLink carries 2 (world-1)/world M N 2 bytes per rank (the one-shot
+ * form carries (world-1) M N 2).  Differences from b2_rowpar_fused:
+ *  - *normed_out receives the address of a context-owned [M, N] bf16 buffer
+ *    (N must equal the context's hidden size).  It is valid until the next
+ *    two-shot call on this context; consume it before that.
+ *  - residual_out is written only for the rows this rank owns, and only those
+ *    rows of residual_in are read:
+ *    the residual stream stays sharded by rows between two-shot calls of the
+ *    same M, which is all the decoder layer needs (reference wiring:
+ *    nanovllm/models/qwen3.py:146-159). */
+int b2_rowpar_fused_twoshot(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias,
+                            int M, int N, int Kr, const void* residual_in, const void* norm_w, float eps,
+                            void** normed_out, void* residual_out, void* stream);
+
 /* ---- RMSNorm: replaces RMSNorm.rms_forward / add_rms_forward
  *      (nanovllm/layers/layernorm.py:16-26, 28-40) ---------------------------
  * x, out: [rows, dim] with row strides ldx / ldo (elements); dim % 8 == 0. */

@@ -26,7 +26,7 @@ _ERR_NAMES = {1: "bad argument", 2: "shape outside what the context was created 
 WAIT_NAMES = {0: "none", 1: "GEMM: TMA stage never filled", 2: "GEMM: stage never freed", 3: "GEMM: accumulator never completed",
               4: "GEMM: accumulator never drained", 5: "fused row-parallel: partial rows never arrived",
               6: "embedding: owner row never arrived", 7: "LM head: a peer's logits never arrived",
-              8: "token broadcast: rank 0's tokens never arrived"}
+              8: "token broadcast: rank 0's tokens never arrived", 9: "two-shot row-parallel: rows owned by other ranks never arrived"}
 
 
 class Config(C.Structure):
@@ -50,6 +50,7 @@ SIGNATURES = {
     "b2_gemm": [_p, _p, _i64, _p, _i64, _p, _p, _i64, _i, _i, _i, _p],
     "b2_gemm_static_scratch": [_p, _i64, _p, _i64, _p, _p, _i64, _i, _i, _i, _p],
     "b2_rowpar_fused": [_p, _p, _i64, _p, _i64, _p, _i, _i, _i, _p, _p, _f, _p, _p, _p],
+    "b2_rowpar_fused_twoshot": [_p, _p, _i64, _p, _i64, _p, _i, _i, _i, _p, _p, _f, C.POINTER(_p), _p, _p],
     "b2_rmsnorm": [_p, _i64, _p, _f, _i, _i, _p, _i64, _p],
     "b2_add_rmsnorm": [_p, _p, _p, _f, _i, _i, _p, _p, _p],
     "b2_store_kvcache": [_p, _i64, _p, _i64, _p, _p, _p, _i, _i, _p],

@@ -21,7 +21,8 @@ enum : int {
   B2_WAIT_PARTIALS = 5,     // fused reduce waiting for partial rows (local or peer)
   B2_WAIT_EMBED = 6,        // embedding waiting for the owner rank's row
   B2_WAIT_LOGITS = 7,       // rank 0 waiting for peers' logits slices
-  B2_WAIT_TOKENS = 8        // a rank waiting for rank 0's sampled tokens
+  B2_WAIT_TOKENS = 8,       // a rank waiting for rank 0's sampled tokens
+  B2_WAIT_ROWS = 9          // two-shot: waiting for the other owners' finished rows
 };
 
 // The bf16 bit pattern that marks "not written yet" in data-as-flag buffers:
@@ -278,8 +279,11 @@ struct b2_ctx {
   // offsets inside the symmetric region
   size_t off_rowpar;    // [2 parity][world][oneshot_tokens][hidden] bf16
   size_t off_embed;     // [2 parity][max_tokens][hidden] bf16
+  size_t off_inbox2;    // two-shot: [2 parity][world][ceil(max_tokens/world)][hidden] bf16 partial rows for the rows this rank owns
   size_t off_logits;    // [max_seqs][vocab] bf16 (used on rank 0)
   size_t off_flags;     // [world] uint32 arrival flags for the logits gather
+  size_t off_out;       // two-shot: [max_tokens][hidden] bf16 normed rows, written by their owner ranks
+  size_t off_rowcnt;    // two-shot: [2 parity] uint32 rows received in off_out
   size_t off_tokens;    // [2 parity][max_seqs] int64 token inbox, -1 = not written
 
   // rank-local scratch

@@ -110,10 +110,17 @@ int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
   off = align_up(off + 2 * W * c->cfg.oneshot_tokens * H * 2, 1024);
   c->off_embed = off;
   if (W > 1) off = align_up(off + 2 * static_cast<size_t>(c->cfg.max_tokens) * H * 2, 1024);
+  c->off_inbox2 = off;
+  const size_t rows_per_rank = ((static_cast<size_t>(c->cfg.max_tokens) + 127) / 128 + W - 1) / W * 128;  // 128-row blocks dealt round-robin
+  if (W > 1) off = align_up(off + 2 * W * rows_per_rank * H * 2, 1024);
   c->off_logits = off;
   if (c->cfg.vocab > 0 && c->cfg.max_seqs > 0) off = align_up(off + static_cast<size_t>(c->cfg.max_seqs) * c->cfg.vocab * 2, 1024);
   c->off_flags = off;
   off = align_up(off + 256, 1024);
+  c->off_out = off;
+  if (W > 1) off = align_up(off + static_cast<size_t>(c->cfg.max_tokens) * H * 2, 1024);
+  c->off_rowcnt = off;
+  off = align_up(off + 64, 1024);
   c->off_tokens = off;
   off = align_up(off + 2 * static_cast<size_t>(c->cfg.max_seqs > 0 ? c->cfg.max_seqs : 1) * 8, 1024);
   c->symm_bytes = off;

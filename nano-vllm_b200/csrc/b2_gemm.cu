@@ -16,6 +16,15 @@
 // CTA that arrives last at the tile's counter reads the sum, re-zeroes the
 // slot and writes the output.  Nobody waits for anybody.
 //
+// EPI_PUSH2: the two-shot form for many tokens.  Token rows are dealt in equal
+// contiguous blocks to the ranks.  The epilogue stores each partial row only
+// into the inbox of the rank that owns it; the owner sums the partials of its
+// rows, adds the residual, normalises, and stores the finished row into every
+// rank's output buffer (symmetric memory), then adds the number of rows it
+// finished to each peer's arrival counter.  A launch ends when its rank has
+// received all rows it does not own.  NVLink carries 2 (tp-1)/tp M N 2 bytes
+// per rank, the minimum for an all-reduce.
+//
 // EPI_PUSH: the fused row-parallel path.  The epilogue rounds the tile to bf16
 // and stores it into the inbox of every rank (its own and, over NVLink, its
 // peers'); then every CTA turns to whole rows of the inbox: it sums the
@@ -23,6 +32,7 @@
 // results.  The inbox is data-as-flag: a slot holds the sentinel until the
 // value lands, and the reader puts the sentinel back after consuming it.
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "b2_common.cuh"
@@ -36,11 +46,13 @@ constexpr int NUM_THREADS = 192;
 constexpr int MAX_ROW_VECS = 6;  // 16-byte vectors of one row per thread in the reduce phase
 constexpr uint64_t PIPE_LIMIT_NS = 1000000000ull;  // no wait inside the GEMM pipeline lasts anywhere near this
 
-enum { EPI_STORE = 0, EPI_PUSH = 1 };
+enum { EPI_STORE = 0, EPI_PUSH = 1, EPI_PUSH2 = 2 };
 
 struct GemmArgs {
   int tilesP, tilesQ, kblocks;
   int gemm_ctas;  // the first gemm_ctas CTAs of the grid share the GEMM units
+  int round_robin;  // 1: whole tiles dealt round-robin instead of a stream-K range
+  int dedicated_reducers;  // two-shot: 1 = the CTAs past gemm_ctas reduce from the start and the GEMM CTAs never do
   int M, N;       // tokens, features of the output
   // EPI_STORE
   uint16_t* C;
@@ -61,6 +73,10 @@ struct GemmArgs {
   uint16_t* residual_out;
   B2DeviceState* dstate;
   uint64_t timeout_ns;
+  // EPI_PUSH2 (inbox / parity_stride / slot_stride then describe the row-owner inbox)
+  unsigned char* outbuf[B2_MAX_WORLD];   // every rank's [max_tokens][hidden] output buffer
+  unsigned int* rowcnt[B2_MAX_WORLD];    // every rank's [2] rows-received counters
+  int rows_per_rank;
   unsigned long long* trace;  // optional [CTA][8][2] (SM clock, global ns) phase stamps; null = off
 };
 
@@ -86,14 +102,51 @@ struct Partition {
 struct Seg {
   int tile, kb0, kb1;
 };
-__device__ __forceinline__ bool next_seg(int& u, int u1, int KB, Seg& s) {
-  if (u >= u1) return false;
-  s.tile = u / KB;
-  s.kb0 = u - s.tile * KB;
-  const int len = min(KB - s.kb0, u1 - u);
-  s.kb1 = s.kb0 + len;
-  u += len;
+
+// The K blocks a CTA works through, by local index i = 0 .. n_units-1.
+//   stream-K   : a contiguous range of the global unit order (tile-major), cut anywhere, also inside a tile
+//   round-robin: whole tiles cta, cta + G, cta + 2G, ... (many-tile problems: the CTAs sweep the token
+//                rows together, front to back, so finished rows become available steadily)
+struct Work {
+  int n_units, u_begin, KB, G, cta;
+  bool rr;
+};
+__device__ __forceinline__ void unit_at(const Work& w, int i, int& tile, int& kb) {
+  if (w.rr) {
+    const int j = i / w.KB;
+    kb = i - j * w.KB;
+    tile = w.cta + j * w.G;
+  } else {
+    const int u = w.u_begin + i;
+    tile = u / w.KB;
+    kb = u - tile * w.KB;
+  }
+}
+__device__ __forceinline__ bool next_seg(const Work& w, int& i, Seg& s) {
+  if (i >= w.n_units) return false;
+  int tile, kb;
+  unit_at(w, i, tile, kb);
+  const int len = min(w.KB - kb, w.n_units - i);
+  s.tile = tile;
+  s.kb0 = kb;
+  s.kb1 = kb + len;
+  i += len;
   return true;
+}
+
+// Two-shot ownership of token rows: blocks of 128 rows are dealt round-robin to the ranks.
+__device__ __forceinline__ int owner_of(int token, int world, int& local_row) {
+  const int b = token >> 7;
+  local_row = ((b / world) << 7) + (token & 127);
+  return b % world;
+}
+__host__ __device__ inline int owned_rows(int M, int world, int rank) {
+  const int blocks = (M + 127) >> 7;
+  const int mine = (blocks - rank + world - 1) / world;  // blocks rank, rank + world, ...
+  if (mine <= 0) return 0;
+  const int last_block = rank + (mine - 1) * world;
+  const int last_rows = (last_block == blocks - 1) ? M - (last_block << 7) : 128;
+  return (mine - 1) * 128 + last_rows;
 }
 
 // ---------------------------------------------------------------------------
@@ -154,6 +207,13 @@ __device__ __forceinline__ void emit_chunk(const GemmArgs& a, float (&v)[32], in
                            b2::pack_bf16(f[6], f[7]));
       if (EPI == EPI_STORE) {
         *reinterpret_cast<uint4*>(a.C + token * a.ldc + feature) = w;
+      } else if (EPI == EPI_PUSH2) {
+        w.x = b2::scrub_sentinel(w.x); w.y = b2::scrub_sentinel(w.y);
+        w.z = b2::scrub_sentinel(w.z); w.w = b2::scrub_sentinel(w.w);
+        int lrow;
+        const int owner = owner_of(token, a.world, lrow);
+        *reinterpret_cast<uint4*>(a.inbox[owner] + parity * a.parity_stride + a.rank * a.slot_stride +
+                                  (static_cast<size_t>(lrow) * a.N + feature) * 2) = w;
       } else {
         w.x = b2::scrub_sentinel(w.x); w.y = b2::scrub_sentinel(w.y);
         w.z = b2::scrub_sentinel(w.z); w.w = b2::scrub_sentinel(w.w);
@@ -181,8 +241,11 @@ __device__ __forceinline__ uint4 pack8f(const float (&f)[8]) {
   return make_uint4(b2::pack_bf16(f[0], f[1]), b2::pack_bf16(f[2], f[3]), b2::pack_bf16(f[4], f[5]), b2::pack_bf16(f[6], f[7]));
 }
 
-template <int S>
-__device__ __forceinline__ void reduce_rows(const GemmArgs& a, unsigned int parity, float* red, volatile int* gave_up) {
+// TWO = false: every rank reduces every row (one-shot); outputs go to normed_out / residual_out.
+// TWO = true : this rank reduces only the rows it owns; a finished row goes into every rank's
+//              output buffer, the new residual stays with the owner.  Returns the rows finished.
+template <int S, bool TWO>
+__device__ __forceinline__ int reduce_rows(const GemmArgs& a, unsigned int parity, float* red, volatile int* gave_up) {
   constexpr int G = S >= 8 ? 2 : (S == 4 ? 3 : MAX_ROW_VECS);  // vectors in flight together: G * S <= 16 loads of 16 bytes
   const int nvec = a.N >> 3;
   const int tid = threadIdx.x;
@@ -190,10 +253,26 @@ __device__ __forceinline__ void reduce_rows(const GemmArgs& a, unsigned int pari
   unsigned char* my = a.inbox[a.rank] + parity * a.parity_stride;
   const uint4 sentinel = make_uint4(B2_SENTINEL32, B2_SENTINEL32, B2_SENTINEL32, B2_SENTINEL32);
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
-  for (int row = blockIdx.x; row < a.M; row += gridDim.x) {
+  // Every CTA takes rows blockIdx, blockIdx + grid, ... once its GEMM work is done.  Two-shot with
+  // dedicated reducers: only the CTAs past the GEMM CTAs reduce; they start at once and follow the GEMM's
+  // sweep over the token rows (worth it only when NVLink, not SM time, bounds the call).
+  int n_rows = a.M, row0 = blockIdx.x, row_step = gridDim.x;
+  if (TWO) {
+    n_rows = owned_rows(a.M, a.world, a.rank);
+    if (a.dedicated_reducers && static_cast<int>(gridDim.x) > a.gemm_ctas) {
+      row0 = static_cast<int>(blockIdx.x) - a.gemm_ctas;
+      row_step = static_cast<int>(gridDim.x) - a.gemm_ctas;
+      if (row0 < 0) row0 = n_rows;  // a GEMM CTA: nothing to reduce
+    }
+  }
+  int rows_done = 0;
+  for (int row = row0; row < n_rows; row += row_step, ++rows_done) {
     float acc[MAX_ROW_VECS][8];
     float ss = 0.f;
-    const size_t row_off = static_cast<size_t>(row) * a.N;
+    const size_t row_off = static_cast<size_t>(row) * a.N;  // row inside the inbox
+    // row of the [M, N] tensors: the owned rows are the 128-row blocks rank, rank + world, ...
+    const int token = TWO ? ((((row >> 7) * a.world + a.rank) << 7) + (row & 127)) : row;
+    const size_t out_off = static_cast<size_t>(token) * a.N;
 #pragma unroll
     for (int g0 = 0; g0 < MAX_ROW_VECS; g0 += G) {
       if (tid + g0 * NUM_THREADS >= nvec) break;
@@ -203,7 +282,7 @@ __device__ __forceinline__ void reduce_rows(const GemmArgs& a, unsigned int pari
 #pragma unroll
       for (int i = 0; i < G; ++i) {
         const int v = tid + (g0 + i) * NUM_THREADS;
-        resv[i] = (with_norm && v < nvec) ? __ldg(reinterpret_cast<const uint4*>(a.residual_in + row_off + v * 8)) : zero4;
+        resv[i] = (with_norm && v < nvec) ? __ldg(reinterpret_cast<const uint4*>(a.residual_in + out_off + v * 8)) : zero4;
       }
       bool pending = true;
       uint64_t t0 = 0;
@@ -251,11 +330,18 @@ __device__ __forceinline__ void reduce_rows(const GemmArgs& a, unsigned int pari
           }
           if (with_norm) {
             add8(acc[g0 + i], resv[i]);
-            *reinterpret_cast<uint4*>(a.residual_out + eoff) = pack8f(acc[g0 + i]);
+            *reinterpret_cast<uint4*>(a.residual_out + out_off + v * 8) = pack8f(acc[g0 + i]);
 #pragma unroll
             for (int e = 0; e < 8; ++e) ss += acc[g0 + i][e] * acc[g0 + i][e];
           } else {
-            *reinterpret_cast<uint4*>(a.normed_out + eoff) = pack8f(acc[g0 + i]);
+            const uint4 y = pack8f(acc[g0 + i]);
+            if (TWO) {
+#pragma unroll
+              for (int r = 0; r < B2_MAX_WORLD; ++r)
+                if (r < a.world) *reinterpret_cast<uint4*>(a.outbuf[r] + (out_off + v * 8) * 2) = y;
+            } else {
+              *reinterpret_cast<uint4*>(a.normed_out + out_off + v * 8) = y;
+            }
           }
         }
       }
@@ -286,10 +372,18 @@ __device__ __forceinline__ void reduce_rows(const GemmArgs& a, unsigned int pari
         o[2] = b2::bf16_round(acc[it][2] * rstd) * b2::bf16_lo(wv[it].y); o[3] = b2::bf16_round(acc[it][3] * rstd) * b2::bf16_hi(wv[it].y);
         o[4] = b2::bf16_round(acc[it][4] * rstd) * b2::bf16_lo(wv[it].z); o[5] = b2::bf16_round(acc[it][5] * rstd) * b2::bf16_hi(wv[it].z);
         o[6] = b2::bf16_round(acc[it][6] * rstd) * b2::bf16_lo(wv[it].w); o[7] = b2::bf16_round(acc[it][7] * rstd) * b2::bf16_hi(wv[it].w);
-        *reinterpret_cast<uint4*>(a.normed_out + row_off + v * 8) = pack8f(o);
+        const uint4 y = pack8f(o);
+        if (TWO) {
+#pragma unroll
+          for (int r = 0; r < B2_MAX_WORLD; ++r)
+            if (r < a.world) *reinterpret_cast<uint4*>(a.outbuf[r] + (out_off + v * 8) * 2) = y;
+        } else {
+          *reinterpret_cast<uint4*>(a.normed_out + out_off + v * 8) = y;
+        }
       }
     }
   }
+  return rows_done;
 }
 
 __device__ __forceinline__ void stamp(const GemmArgs& a, int slot) {
@@ -330,8 +424,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   Partition part;
   part.base = U / a.gemm_ctas;
   part.rem = U % a.gemm_ctas;
-  const int u_begin = has_gemm ? part.u0(cta) : 0;
-  const int u_end = has_gemm ? part.u0(cta + 1) : 0;
+  Work work;
+  work.KB = KB;
+  work.G = a.gemm_ctas;
+  work.cta = cta;
+  work.rr = a.round_robin != 0;
+  work.u_begin = has_gemm ? part.u0(cta) : 0;
+  if (!has_gemm) work.n_units = 0;
+  else if (work.rr) work.n_units = ((tiles - cta + a.gemm_ctas - 1) / a.gemm_ctas) * KB;
+  else work.n_units = part.u0(cta + 1) - work.u_begin;
 
   if (threadIdx.x == 0) {
     stamp(a, 7);
@@ -367,12 +468,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
       if (lane == 0) {
         const uint64_t polP = SWAP ? b2::kEvictFirst : b2::kEvictNormal;
         const uint64_t polQ = SWAP ? b2::kEvictLast : b2::kEvictNormal;
-        const int n_units = u_end - u_begin;
+        const int n_units = work.n_units;
         const int pre = n_units < STAGES ? n_units : STAGES;
         // The weight tiles of the first stages depend on no earlier kernel: fetch them before the
         // dependency wait, so that they are in flight (or landed) when the activations become valid.
         for (int i = 0; i < pre; ++i) {
-          const int u = u_begin + i, tile = u / KB, kb = u - tile * KB;
+          int tile, kb;
+          unit_at(work, i, tile, kb);
           const int tp = tile / a.tilesQ, tq = tile - tp * a.tilesQ;
           const uint32_t fb = bar_full + i * 8;
           b2::mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
@@ -383,7 +485,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
         b2::pdl_wait();
         stamp(a, 3);
         for (int i = 0; i < pre; ++i) {
-          const int u = u_begin + i, tile = u / KB, kb = u - tile * KB;
+          int tile, kb;
+          unit_at(work, i, tile, kb);
           const int tp = tile / a.tilesQ, tq = tile - tp * a.tilesQ;
           const uint32_t fb = bar_full + i * 8;
           const uint32_t dst = smem_base + i * C::STAGE_BYTES;
@@ -393,7 +496,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
         int stage = pre == STAGES ? 0 : pre;
         uint32_t phase = pre == STAGES ? 1 : 0;
         for (int i = pre; i < n_units; ++i) {
-          const int u = u_begin + i, tile = u / KB, kb = u - tile * KB;
+          int tile, kb;
+          unit_at(work, i, tile, kb);
           const int tp = tile / a.tilesQ, tq = tile - tp * a.tilesQ;
           if (!b2::mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_SMEM_EMPTY)) break;
           const uint32_t fb = bar_full + stage * 8;
@@ -410,10 +514,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
         constexpr uint32_t idesc = b2::umma_idesc_bf16(BN);
         int stage = 0;
         uint32_t phase = 0;
-        int u = u_begin, seg = 0;
+        int u = 0, seg = 0;
         Seg s;
         bool ok = true;
-        while (ok && next_seg(u, u_end, KB, s)) {
+        while (ok && next_seg(work, u, s)) {
           const int acc = seg & 1;
           const uint32_t use = static_cast<uint32_t>(seg >> 1);  // how often this accumulator was used before
           if (!b2::mbar_wait(bar_tempty + acc * 8, (use & 1) ^ 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_TMEM_EMPTY)) break;
@@ -444,10 +548,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
       // ---------------- epilogue warps ----------------
       const int q = warp & 3;  // TMEM lane quadrant this warp may read
       b2::pdl_wait();
-      if (EPI == EPI_PUSH) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
-      int u = u_begin, seg = 0;
+      if (EPI != EPI_STORE) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
+      int u = 0, seg = 0;
       Seg s;
-      while (next_seg(u, u_end, KB, s)) {
+      while (next_seg(work, u, s)) {
         const int acc = seg & 1;
         const uint32_t use = static_cast<uint32_t>(seg >> 1);
         if (!b2::mbar_wait(bar_tfull + acc * 8, use & 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_TMEM_FULL)) break;
@@ -520,7 +624,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
 
   // ---- all roles meet; tensor memory goes back ------------------------------
   b2::pdl_wait();
-  if (EPI == EPI_PUSH) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
+  if (EPI != EPI_STORE) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
   __syncwarp();
   b2::tc_fence_before();
   __syncthreads();
@@ -534,13 +638,47 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   if (warp == 1 && has_gemm) b2::tmem_dealloc(tmem_base, C::TMEM_COLS);
 
   if (threadIdx.x == 0) stamp(a, 5);
-  if (EPI == EPI_PUSH) {
+  if (EPI != EPI_STORE) {
     if (!aborted) {
-      switch (a.world) {
-        case 1: reduce_rows<1>(a, parity, red, abort_flag); break;
-        case 2: reduce_rows<2>(a, parity, red, abort_flag); break;
-        case 4: reduce_rows<4>(a, parity, red, abort_flag); break;
-        default: reduce_rows<8>(a, parity, red, abort_flag); break;
+      if (EPI == EPI_PUSH) {
+        switch (a.world) {
+          case 1: reduce_rows<1, false>(a, parity, red, abort_flag); break;
+          case 2: reduce_rows<2, false>(a, parity, red, abort_flag); break;
+          case 4: reduce_rows<4, false>(a, parity, red, abort_flag); break;
+          default: reduce_rows<8, false>(a, parity, red, abort_flag); break;
+        }
+      } else {
+        int rows_done = 0;
+        switch (a.world) {
+          case 2: rows_done = reduce_rows<2, true>(a, parity, red, abort_flag); break;
+          case 4: rows_done = reduce_rows<4, true>(a, parity, red, abort_flag); break;
+          default: rows_done = reduce_rows<8, true>(a, parity, red, abort_flag); break;
+        }
+        // the finished rows must be visible on every GPU before their count is
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0 && rows_done > 0) {
+          for (int r = 0; r < a.world; ++r)
+            if (r != a.rank)
+              asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a.rowcnt[r] + parity), "r"(static_cast<unsigned int>(rows_done)) : "memory");
+        }
+        // one CTA holds the launch open until the rows owned elsewhere have all arrived here
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+          const int mine = owned_rows(a.M, a.world, a.rank);
+          const unsigned int expect = static_cast<unsigned int>(a.M - mine);
+          unsigned int* cnt = a.rowcnt[a.rank] + parity;
+          const uint64_t t0 = b2::globaltimer_ns();
+          for (uint32_t spin = 0;; ++spin) {
+            unsigned int got;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(cnt) : "memory");
+            if (got >= expect) break;
+            if ((spin & 0xFF) == 0xFF && b2::globaltimer_ns() - t0 > a.timeout_ns) {
+              b2::report_timeout(a.status, B2_WAIT_ROWS);
+              break;
+            }
+          }
+          *reinterpret_cast<volatile unsigned int*>(cnt) = 0;  // next used two launches from now, after every peer has seen this launch end
+        }
       }
     }
     // the last CTA to finish advances the launch parity for the next call
@@ -577,7 +715,7 @@ int launch_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmArgs& 
 template <int EPI>
 int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K, GemmArgs& args,
                 int min_grid, cudaStream_t stream) {
-  const bool swap = M <= 256;
+  const bool swap = (EPI != EPI_PUSH2) && M <= 256;
   int bn;
   if (swap) bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   else bn = (N >= 256) ? 256 : (N > 64 ? 128 : 64);
@@ -597,10 +735,23 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
   if (U > (1ll << 30)) return B2_ERR_SHAPE;
   // every CTA should stream at least ~8 K blocks, or splitting costs more than it saves
   int64_t g = std::max<int64_t>(1, U / 8);
-  g = std::min<int64_t>(g, ctx->num_sms);
+  int sms_for_gemm = ctx->num_sms;
+  if (EPI == EPI_PUSH2) {
+    // B2_TWOSHOT_REDUCERS=n sets n CTAs aside that only reduce, following the GEMM's sweep over the rows, so
+    // that the second half of the NVLink traffic overlaps the tensor-core work.  Default 0: every CTA reduces
+    // after its GEMM work (SM time, not NVLink, bounds most shapes, and then setting CTAs aside only costs)
+    static const int reducers = [] {
+      const char* e = getenv("B2_TWOSHOT_REDUCERS");
+      return e != nullptr ? atoi(e) : 0;
+    }();
+    args.dedicated_reducers = reducers > 0 ? 1 : 0;
+    sms_for_gemm = std::max(1, ctx->num_sms - std::max(0, reducers));
+  }
+  g = std::min<int64_t>(g, sms_for_gemm);
   g = std::min<int64_t>(g, U);
   args.gemm_ctas = static_cast<int>(g);
-  const int grid = std::max(args.gemm_ctas, std::min(min_grid, ctx->num_sms));
+  args.round_robin = (!swap && tiles >= 4 * g) ? 1 : 0;
+  const int grid = (EPI == EPI_PUSH2) ? ctx->num_sms : std::max(args.gemm_ctas, std::min(min_grid, ctx->num_sms));
 
   CUtensorMap tmP, tmQ;
   const void* pP = swap ? W : A;
@@ -611,12 +762,14 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
   rc = b2::encode_tmap_2d(&tmQ, pQ, K, rowsQ, ldQ, BK, bn);
   if (rc != B2_OK) return rc;
 
-  if (swap) {
-    switch (bn) {
-      case 32: return launch_inst<32, true, EPI>(tmP, tmQ, args, grid, stream);
-      case 64: return launch_inst<64, true, EPI>(tmP, tmQ, args, grid, stream);
-      case 128: return launch_inst<128, true, EPI>(tmP, tmQ, args, grid, stream);
-      default: return launch_inst<256, true, EPI>(tmP, tmQ, args, grid, stream);
+  if constexpr (EPI != EPI_PUSH2) {
+    if (swap) {
+      switch (bn) {
+        case 32: return launch_inst<32, true, EPI>(tmP, tmQ, args, grid, stream);
+        case 64: return launch_inst<64, true, EPI>(tmP, tmQ, args, grid, stream);
+        case 128: return launch_inst<128, true, EPI>(tmP, tmQ, args, grid, stream);
+        default: return launch_inst<256, true, EPI>(tmP, tmQ, args, grid, stream);
+      }
     }
   }
   switch (bn) {
@@ -731,6 +884,45 @@ int b2_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw,
   args.ldc = ldc;
   args.bias = static_cast<const uint16_t*>(bias);
   return launch_gemm<EPI_STORE>(ctx, A, lda, W, ldw, M, N, K, args, 0, static_cast<cudaStream_t>(stream));
+}
+
+int b2_rowpar_fused_twoshot(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias, int M, int N, int Kr,
+                            const void* residual_in, const void* norm_w, float eps, void** normed_out, void* residual_out, void* stream) {
+  if (ctx == nullptr || normed_out == nullptr) return B2_ERR_ARG;
+  *normed_out = nullptr;
+  int rc = check_operands(A, lda, W, ldw, M, N, Kr);
+  if (rc != B2_OK) return rc;
+  if (ctx->cfg.world < 2) return b2::set_error(B2_ERR_STATE, "b2_rowpar_fused_twoshot needs a tensor-parallel size of 2 or more");
+  if (!ctx->peers_ready) return B2_ERR_STATE;
+  if (M > ctx->cfg.max_tokens || N != ctx->cfg.hidden || N > MAX_ROW_VECS * NUM_THREADS * 8)
+    return b2::set_error(B2_ERR_SHAPE, "b2_rowpar_fused_twoshot: M = %d (limit %d), N = %d (must equal the context's hidden size %d)", M,
+                         ctx->cfg.max_tokens, N, ctx->cfg.hidden);
+  *normed_out = ctx->symm + ctx->off_out;
+  if (M == 0) return B2_OK;
+  if (norm_w != nullptr && (!residual_in || !residual_out || !aligned16(residual_in) || !aligned16(residual_out) || !aligned16(norm_w)))
+    return B2_ERR_ARG;
+  if (bias != nullptr && !aligned16(bias)) return B2_ERR_ARG;
+  const int world = ctx->cfg.world;
+  GemmArgs args{};
+  args.bias = (ctx->cfg.rank == 0) ? static_cast<const uint16_t*>(bias) : nullptr;
+  args.rows_per_rank = owned_rows(M, world, 0);
+  const size_t max_rows = ((static_cast<size_t>(ctx->cfg.max_tokens) + 127) / 128 + world - 1) / world * 128;
+  args.slot_stride = max_rows * ctx->cfg.hidden * 2;
+  args.parity_stride = args.slot_stride * world;
+  for (int r = 0; r < world; ++r) {
+    args.inbox[r] = ctx->peer[r] + ctx->off_inbox2;
+    args.outbuf[r] = ctx->peer[r] + ctx->off_out;
+    args.rowcnt[r] = reinterpret_cast<unsigned int*>(ctx->peer[r] + ctx->off_rowcnt);
+  }
+  args.world = world;
+  args.rank = ctx->cfg.rank;
+  args.residual_in = static_cast<const uint16_t*>(residual_in);
+  args.norm_w = static_cast<const uint16_t*>(norm_w);
+  args.eps = eps;
+  args.residual_out = static_cast<uint16_t*>(residual_out);
+  args.dstate = ctx->dstate;
+  args.timeout_ns = static_cast<uint64_t>(ctx->cfg.timeout_ms) * 1000000ull;
+  return launch_gemm<EPI_PUSH2>(ctx, A, lda, W, ldw, M, N, Kr, args, args.rows_per_rank, static_cast<cudaStream_t>(stream));
 }
 
 int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias, int M, int N, int Kr,

@@ -46,27 +46,43 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> 
     return out.view(*lead, N)
 
 
+TWO_SHOT_MIN_TOKENS = 257  # from this many tokens on (and tensor-parallel size >= 2) the two-shot kernel is used
+
+
 def rowpar_fused(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, residual: torch.Tensor | None,
                  norm_w: torch.Tensor | None, eps: float):
     """Row-parallel GEMM + all-reduce (+ residual add + RMSNorm when norm_w is given).
-    Returns y, or (normed, new_residual)."""
+    Returns y, or (normed, new_residual).
+
+    For many tokens at tensor-parallel size >= 2 the two-shot kernel runs: `normed` is then a view of a
+    buffer owned by the runtime (valid until the next such call) and `new_residual` holds only the rows
+    this rank owns (128-row blocks rank, rank + world, ...); the next fused call reads exactly those rows."""
     x2 = _as2d(_bf16_rows(x, "row-parallel input"))
     if x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
         x2 = x2.contiguous()
     M, Kr = x2.shape
     N = w.shape[0]
-    out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    rt = get_runtime()
     res_out = None
     if norm_w is not None:
         residual = _bf16_rows(residual, "residual")
         if not residual.is_contiguous():
             residual = residual.contiguous()
         res_out = torch.empty_like(residual)
+    args_tail = (residual.data_ptr() if norm_w is not None else None, norm_w.data_ptr() if norm_w is not None else None, float(eps))
+    if rt.world >= 2 and M >= TWO_SHOT_MIN_TOKENS and N == rt.hidden and M <= rt.max_tokens:
+        ptr = C.c_void_p()
+        _abi.check(_lib.b2_rowpar_fused_twoshot(rt.ctx, x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0),
+                                                bias.data_ptr() if bias is not None else None, M, N, Kr, *args_tail, C.byref(ptr),
+                                                res_out.data_ptr() if res_out is not None else None, _stream()), "b2_rowpar_fused_twoshot")
+        out = _library_view(ptr.value, (M, N), x.device)
+        if norm_w is None:
+            return out.clone().view(*x.shape[:-1], N)  # a plain forward hands out memory the caller may keep
+        return out, res_out
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
     if M:
-        _abi.check(_lib.b2_rowpar_fused(get_runtime().ctx, x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0),
-                                        bias.data_ptr() if bias is not None else None, M, N, Kr,
-                                        residual.data_ptr() if norm_w is not None else None,
-                                        norm_w.data_ptr() if norm_w is not None else None, float(eps), out.data_ptr(),
+        _abi.check(_lib.b2_rowpar_fused(rt.ctx, x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0),
+                                        bias.data_ptr() if bias is not None else None, M, N, Kr, *args_tail, out.data_ptr(),
                                         res_out.data_ptr() if res_out is not None else None, _stream()), "b2_rowpar_fused")
     if norm_w is None:
         return out.view(*x.shape[:-1], N)
@@ -155,6 +171,16 @@ class _DevicePtr:
 
 
 _LOGIT_VIEWS: dict = {}
+
+
+def _library_view(ptr: int, shape: tuple[int, int], device) -> torch.Tensor:
+    """bf16 tensor over memory the library owns; built once per (address, shape), outside any graph capture."""
+    key = (ptr, *shape)
+    view = _LOGIT_VIEWS.get(key)
+    if view is None:
+        view = torch.as_tensor(_DevicePtr(ptr, shape), device=device).view(torch.bfloat16)
+        _LOGIT_VIEWS[key] = view
+    return view
 
 
 def lm_head(h: torch.Tensor, w: torch.Tensor, row_index: torch.Tensor | None):

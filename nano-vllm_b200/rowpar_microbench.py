@@ -12,7 +12,7 @@ Stand-alone, under torchrun with N ranks, it runs the Qwen3-32B shapes
 M in {1, 8, 64, 256, 1024, 8192} and prints one JSON row per case:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        nano-vllm_b200/rowpar_microbench.py [--m 1,8,64] [--no-nccl]
+        nano-vllm_b200/rowpar_microbench.py [--tokens 1,8,64] [--no-nccl]
 """
 from __future__ import annotations
 
@@ -126,7 +126,7 @@ def main():
     from nanovllm_b200 import rowpar_microbench as mb  # the package-relative copy of this module
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("--m", default="1,8,64,256,1024,8192")
+    ap.add_argument("--tokens", default="1,8,64,256,1024,8192")
     ap.add_argument("--no-nccl", action="store_true")
     ap.add_argument("--iters", type=int, default=200)
     a = ap.parse_args()
@@ -140,7 +140,7 @@ def main():
     p = os.path.join(os.path.dirname(here), "MEASURED_PEAKS.json")
     if os.path.exists(p):
         peaks = json.load(open(p))
-    ms = [int(v) for v in a.m.split(",")]
+    ms = [int(v) for v in a.tokens.split(",")]
     init_runtime(max_tokens=max(ms), hidden=5120, oneshot_tokens=1024)
     try:
         for proj, k_total in (("o_proj", 8192), ("down_proj", 25600)):

@@ -27,7 +27,7 @@ def _worker(rank: int, world: int, port: int):
     from tests.gpu_util import assert_close_bf16, ulp_mismatch_fraction
     dev = torch.device("cuda", rank)
     vocab = 4096 * world
-    rt = init_runtime(max_tokens=2048, hidden=5120, oneshot_tokens=512, vocab=vocab, max_seqs=64)
+    rt = init_runtime(max_tokens=4096, hidden=5120, oneshot_tokens=512, vocab=vocab, max_seqs=64)
     try:
         # ---- fused row-parallel block: shapes follow each other without a host sync ----
         shapes = [(64, 4096, 4096), (1, 2048, 1024), (8, 8192, 5120), (64, 12288, 4096), (200, 1024, 5120), (512, 2048, 1024),
@@ -53,6 +53,30 @@ def _worker(rank: int, world: int, port: int):
         gathered = [None] * world
         dist.all_gather_object(gathered, probe)
         assert all(g == gathered[0] for g in gathered), gathered
+
+        # ---- two-shot form (many tokens): normed rows everywhere, the residual only on the rows a rank owns ----
+        for i, (m, k) in enumerate([(1024, 2048), (300, 1024), (4096, 1024), (777, 2048)]):
+            n = 5120
+            xs, ws, residual, norm_w = O.rowpar_case(m, k, n, world, seed=300 + i)
+            for _ in range(2):
+                normed, new_res = ops.rowpar_fused(xs[rank].to(dev), ws[rank].to(dev), None, residual.to(dev), norm_w.to(dev), 1e-6)
+            torch.cuda.synchronize()
+            rt.check_status()
+            exact_n, exact_s = O.fused_row_parallel_norm_exact(xs, ws, residual, norm_w, 1e-6)
+            assert_close_bf16(normed, exact_n, f"rank {rank} two-shot normed M={m}")
+            mine = (torch.arange(m) // 128) % world == rank  # 128-row blocks are dealt round-robin
+            assert_close_bf16(new_res.cpu()[mine], exact_s[mine], f"rank {rank} two-shot residual (owned rows)")
+            # row-sharded residual feeds the next call: chain a second block on the first one's outputs
+            xs2, ws2, _, norm_w2 = O.rowpar_case(m, k, n, world, seed=400 + i)
+            normed2, res2 = ops.rowpar_fused(xs2[rank].to(dev), ws2[rank].to(dev), None, new_res, norm_w2.to(dev), 1e-6)
+            torch.cuda.synchronize()
+            y2 = sum(x.float() @ w.float().t() for x, w in zip(xs2, ws2))
+            s2 = y2 + exact_s.bfloat16().float()
+            n2 = s2 * torch.rsqrt(s2.pow(2).mean(-1, keepdim=True) + 1e-6) * norm_w2.float()
+            assert_close_bf16(normed2, n2, f"rank {rank} chained two-shot normed M={m}", abs_tol=4e-2, rel_tol=1e-2)
+        y = ops.rowpar_fused(xs[rank].to(dev), ws[rank].to(dev), None, None, None, 0.0)  # plain forward through the two-shot kernel
+        assert_close_bf16(y, sum(x.float() @ w.float().t() for x, w in zip(xs, ws)), "two-shot plain forward")
+        rt.check_status()
 
         # ---- plain RowParallelLinear.forward with a bias (added once, by rank 0) ----
         xs, ws, _, _ = O.rowpar_case(48, 1024, 1024, world, seed=7)
