@@ -156,7 +156,7 @@ int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int6
 
 /* The same block in its two-shot form, for many tokens (M above a few hundred)
  * at tensor-parallel size >= 2.  Token rows are dealt to the ranks in blocks
- * of 128 rows, round-robin (rank r owns rows [128 b, 128 b + 128) for
+ * of 16 rows, round-robin (rank r owns rows [16 b, 16 b + 16) for
  * b = r, r + world, ...).  Each rank's GEMM epilogue sends
  * a partial row only to the rank that owns it; the owner reduces, adds the
  * residual, normalises and stores the finished row into every rank's output

@@ -111,7 +111,7 @@ int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
   c->off_embed = off;
   if (W > 1) off = align_up(off + 2 * static_cast<size_t>(c->cfg.max_tokens) * H * 2, 1024);
   c->off_inbox2 = off;
-  const size_t rows_per_rank = ((static_cast<size_t>(c->cfg.max_tokens) + 127) / 128 + W - 1) / W * 128;  // 128-row blocks dealt round-robin
+  const size_t rows_per_rank = ((static_cast<size_t>(c->cfg.max_tokens) + 15) / 16 + W - 1) / W * 16;  // 16-row blocks dealt round-robin
   if (W > 1) off = align_up(off + 2 * W * rows_per_rank * H * 2, 1024);
   c->off_logits = off;
   if (c->cfg.vocab > 0 && c->cfg.max_seqs > 0) off = align_up(off + static_cast<size_t>(c->cfg.max_seqs) * c->cfg.vocab * 2, 1024);

@@ -88,6 +88,7 @@ struct Cfg {
   static constexpr int STAGES = (196608 / STAGE_BYTES) > 8 ? 8 : (196608 / STAGE_BYTES);
   static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr uint32_t SMEM_BYTES_ROWS = SMEM_BYTES + 4 * 8192 /*epilogue staging of the token-row layout*/;
 };
 
 struct Partition {
@@ -134,19 +135,20 @@ __device__ __forceinline__ bool next_seg(const Work& w, int& i, Seg& s) {
   return true;
 }
 
-// Two-shot ownership of token rows: blocks of 128 rows are dealt round-robin to the ranks.
+// Two-shot ownership of token rows: blocks of 16 rows are dealt round-robin to the ranks.
+constexpr int OWN_SHIFT = 4, OWN_ROWS = 1 << OWN_SHIFT;
 __device__ __forceinline__ int owner_of(int token, int world, int& local_row) {
-  const int b = token >> 7;
-  local_row = ((b / world) << 7) + (token & 127);
+  const int b = token >> OWN_SHIFT;
+  local_row = ((b / world) << OWN_SHIFT) + (token & (OWN_ROWS - 1));
   return b % world;
 }
 __host__ __device__ inline int owned_rows(int M, int world, int rank) {
-  const int blocks = (M + 127) >> 7;
+  const int blocks = (M + OWN_ROWS - 1) >> OWN_SHIFT;
   const int mine = (blocks - rank + world - 1) / world;  // blocks rank, rank + world, ...
   if (mine <= 0) return 0;
   const int last_block = rank + (mine - 1) * world;
-  const int last_rows = (last_block == blocks - 1) ? M - (last_block << 7) : 128;
-  return (mine - 1) * 128 + last_rows;
+  const int last_rows = (last_block == blocks - 1) ? M - (last_block << OWN_SHIFT) : OWN_ROWS;
+  return (mine - 1) * OWN_ROWS + last_rows;
 }
 
 // ---------------------------------------------------------------------------
@@ -154,76 +156,113 @@ __host__ __device__ inline int owned_rows(int M, int world, int rank) {
 // (row of the P tile) q*32 + lane and columns c*32 .. c*32+31 (rows of the Q
 // tile).
 // ---------------------------------------------------------------------------
-template <bool SWAP, int EPI>
-__device__ __forceinline__ void emit_chunk(const GemmArgs& a, float (&v)[32], int p_row, int q_row0, int lane,
-                                           unsigned int parity) {
-  if (SWAP) {
-    const int feature = p_row;
+// NC columns (tokens token0 ..) of one feature per lane, features = consecutive lanes.
+// Lanes 2i and 2i+1 hold features f and f+1 of the same tokens.  They swap
+// halves so that each lane stores a packed (f, f+1) pair: the even lane for
+// even columns, the odd lane for odd columns.
+template <int NC, int EPI>
+__device__ __forceinline__ void emit_feature_lanes(const GemmArgs& a, float (&v)[NC], int feature, int token0, int lane,
+                                                   unsigned int parity) {
+  if (a.bias != nullptr && feature < a.N) {
+    const float b = __uint_as_float(static_cast<uint32_t>(a.bias[feature]) << 16);
+#pragma unroll
+    for (int j = 0; j < NC; ++j) v[j] += b;
+  }
+  const int fbase = feature & ~1;
+  const bool odd = lane & 1;
+#pragma unroll
+  for (int j = 0; j < NC; j += 2) {
+    const float send = odd ? v[j] : v[j + 1];
+    const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+    const int token = token0 + j + (odd ? 1 : 0);
+    uint32_t w = odd ? b2::pack_bf16(recv, v[j + 1]) : b2::pack_bf16(v[j], recv);
+    if (token < a.M && fbase < a.N) {
+      if (EPI == EPI_STORE) {
+        *reinterpret_cast<uint32_t*>(a.C + token * a.ldc + fbase) = w;
+      } else {
+        w = b2::scrub_sentinel(w);
+        const size_t off = parity * a.parity_stride + a.rank * a.slot_stride +
+                           (static_cast<size_t>(token) * a.N + fbase) * 2;
+#pragma unroll
+        for (int r = 0; r < B2_MAX_WORLD; ++r)
+          if (r < a.world) *reinterpret_cast<uint32_t*>(a.inbox[r] + off) = w;
+      }
+    }
+  }
+}
+
+// Token-row epilogue (SWAP = false): a lane holds 32 consecutive features of one token row.  Storing them
+// straight from registers would make every store instruction touch 32 different rows with 16 bytes each,
+// which wastes NVLink packets when the destination is a peer.  Instead each warp parks up to 4 chunks
+// (128 features = 256 bytes per row) in its own 8 KB of shared memory (16-byte pieces XOR-swizzled by row)
+// and then writes whole 256-byte row segments, two rows per instruction.
+constexpr int STAGE_ROW_BYTES = 256;
+constexpr int STAGING_BYTES_PER_WARP = 32 * STAGE_ROW_BYTES;
+
+__device__ __forceinline__ void stage_row_chunk(const GemmArgs& a, unsigned char* wbuf, int lane, int slot, float (&v)[32], int feature0,
+                                                bool scrub) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int feature = feature0 + g * 8;
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = v[g * 8 + e];
     if (a.bias != nullptr && feature < a.N) {
-      const float b = __uint_as_float(static_cast<uint32_t>(a.bias[feature]) << 16);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] += b;
+      const uint4 bv = *reinterpret_cast<const uint4*>(a.bias + feature);
+      f[0] += b2::bf16_lo(bv.x); f[1] += b2::bf16_hi(bv.x); f[2] += b2::bf16_lo(bv.y); f[3] += b2::bf16_hi(bv.y);
+      f[4] += b2::bf16_lo(bv.z); f[5] += b2::bf16_hi(bv.z); f[6] += b2::bf16_lo(bv.w); f[7] += b2::bf16_hi(bv.w);
     }
-    // Lanes 2i and 2i+1 hold features f and f+1 of the same tokens.  They swap
-    // halves so that each lane stores a packed (f, f+1) pair: the even lane for
-    // even columns, the odd lane for odd columns.
-    const int fbase = feature & ~1;
-    const bool odd = lane & 1;
-#pragma unroll
-    for (int j = 0; j < 32; j += 2) {
-      const float send = odd ? v[j] : v[j + 1];
-      const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
-      const int token = q_row0 + j + (odd ? 1 : 0);
-      uint32_t w = odd ? b2::pack_bf16(recv, v[j + 1]) : b2::pack_bf16(v[j], recv);
-      if (token < a.M && fbase < a.N) {
-        if (EPI == EPI_STORE) {
-          *reinterpret_cast<uint32_t*>(a.C + token * a.ldc + fbase) = w;
-        } else {
-          w = b2::scrub_sentinel(w);
-          const size_t off = parity * a.parity_stride + a.rank * a.slot_stride +
-                             (static_cast<size_t>(token) * a.N + fbase) * 2;
-#pragma unroll
-          for (int r = 0; r < B2_MAX_WORLD; ++r)
-            if (r < a.world) *reinterpret_cast<uint32_t*>(a.inbox[r] + off) = w;
-        }
-      }
+    uint4 w = make_uint4(b2::pack_bf16(f[0], f[1]), b2::pack_bf16(f[2], f[3]), b2::pack_bf16(f[4], f[5]), b2::pack_bf16(f[6], f[7]));
+    if (scrub) {
+      w.x = b2::scrub_sentinel(w.x); w.y = b2::scrub_sentinel(w.y);
+      w.z = b2::scrub_sentinel(w.z); w.w = b2::scrub_sentinel(w.w);
     }
-  } else {
-    const int token = p_row;
-    if (token >= a.M) return;
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      const int feature = q_row0 + g * 8;
-      if (feature >= a.N) break;
-      float f[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = v[g * 8 + e];
-      if (a.bias != nullptr) {
-        const uint4 bv = *reinterpret_cast<const uint4*>(a.bias + feature);
-        f[0] += b2::bf16_lo(bv.x); f[1] += b2::bf16_hi(bv.x); f[2] += b2::bf16_lo(bv.y); f[3] += b2::bf16_hi(bv.y);
-        f[4] += b2::bf16_lo(bv.z); f[5] += b2::bf16_hi(bv.z); f[6] += b2::bf16_lo(bv.w); f[7] += b2::bf16_hi(bv.w);
-      }
-      uint4 w = make_uint4(b2::pack_bf16(f[0], f[1]), b2::pack_bf16(f[2], f[3]), b2::pack_bf16(f[4], f[5]),
-                           b2::pack_bf16(f[6], f[7]));
+    const int piece = slot * 4 + g;
+    *reinterpret_cast<uint4*>(wbuf + lane * STAGE_ROW_BYTES + ((piece ^ (lane & 15)) << 4)) = w;
+  }
+}
+
+template <int EPI>
+__device__ __forceinline__ void flush_rows(const GemmArgs& a, unsigned char* wbuf, int lane, int token0, int feature0, int npieces,
+                                           unsigned int parity) {
+  __syncwarp();
+  const int piece = lane & 15;
+  const int feature = feature0 + piece * 8;
+#pragma unroll 4
+  for (int it = 0; it < 16; ++it) {
+    const int row = it * 2 + (lane >> 4);
+    const int token = token0 + row;
+    if (piece < npieces && token < a.M && feature < a.N) {
+      const uint4 w = *reinterpret_cast<const uint4*>(wbuf + row * STAGE_ROW_BYTES + ((piece ^ (row & 15)) << 4));
       if (EPI == EPI_STORE) {
         *reinterpret_cast<uint4*>(a.C + token * a.ldc + feature) = w;
       } else if (EPI == EPI_PUSH2) {
-        w.x = b2::scrub_sentinel(w.x); w.y = b2::scrub_sentinel(w.y);
-        w.z = b2::scrub_sentinel(w.z); w.w = b2::scrub_sentinel(w.w);
         int lrow;
         const int owner = owner_of(token, a.world, lrow);
         *reinterpret_cast<uint4*>(a.inbox[owner] + parity * a.parity_stride + a.rank * a.slot_stride +
                                   (static_cast<size_t>(lrow) * a.N + feature) * 2) = w;
       } else {
-        w.x = b2::scrub_sentinel(w.x); w.y = b2::scrub_sentinel(w.y);
-        w.z = b2::scrub_sentinel(w.z); w.w = b2::scrub_sentinel(w.w);
-        const size_t off = parity * a.parity_stride + a.rank * a.slot_stride +
-                           (static_cast<size_t>(token) * a.N + feature) * 2;
+        const size_t off = parity * a.parity_stride + a.rank * a.slot_stride + (static_cast<size_t>(token) * a.N + feature) * 2;
 #pragma unroll
         for (int r = 0; r < B2_MAX_WORLD; ++r)
           if (r < a.world) *reinterpret_cast<uint4*>(a.inbox[r] + off) = w;
       }
     }
+  }
+  __syncwarp();
+}
+
+// One 32-column chunk c of a tile leaves the registers.  Feature-lane layout (SWAP): stored at once.
+// Token-row layout: parked in the warp's staging buffer; every fourth chunk (and the tile's last) flushes.
+template <int BN, bool SWAP, int EPI>
+__device__ __forceinline__ void emit_chunk(const GemmArgs& a, float (&v)[32], int p_row, int q_tile0, int c, int lane, unsigned int parity,
+                                           unsigned char* wbuf) {
+  if (SWAP) {
+    emit_feature_lanes<32, EPI>(a, v, p_row, q_tile0 + c * 32, lane, parity);
+  } else {
+    stage_row_chunk(a, wbuf, lane, c & 3, v, q_tile0 + c * 32, EPI != EPI_STORE);
+    if ((c & 3) == 3 || c == BN / 32 - 1)
+      flush_rows<EPI>(a, wbuf, lane, p_row - lane, q_tile0 + (c & ~3) * 32, ((c & 3) + 1) * 4, parity);
   }
 }
 
@@ -270,8 +309,8 @@ __device__ __forceinline__ int reduce_rows(const GemmArgs& a, unsigned int parit
     float acc[MAX_ROW_VECS][8];
     float ss = 0.f;
     const size_t row_off = static_cast<size_t>(row) * a.N;  // row inside the inbox
-    // row of the [M, N] tensors: the owned rows are the 128-row blocks rank, rank + world, ...
-    const int token = TWO ? ((((row >> 7) * a.world + a.rank) << 7) + (row & 127)) : row;
+    // row of the [M, N] tensors: the owned rows are the 16-row blocks rank, rank + world, ...
+    const int token = TWO ? ((((row >> OWN_SHIFT) * a.world + a.rank) << OWN_SHIFT) + (row & (OWN_ROWS - 1))) : row;
     const size_t out_off = static_cast<size_t>(token) * a.N;
 #pragma unroll
     for (int g0 = 0; g0 < MAX_ROW_VECS; g0 += G) {
@@ -391,6 +430,69 @@ __device__ __forceinline__ void stamp(const GemmArgs& a, int slot) {
     unsigned long long* t = a.trace + (static_cast<size_t>(blockIdx.x) * 8 + slot) * 2;
     t[0] = static_cast<unsigned long long>(clock64());
     t[1] = b2::globaltimer_ns();
+  }
+}
+
+// What follows the GEMM part of a fused row-parallel launch: the reduce phase (one-shot: all rows; two-shot:
+// owned rows, then the arrival count of finished rows) and the advance of the launch parity.
+template <int EPI>
+__device__ __forceinline__ void fused_tail(const GemmArgs& a, unsigned int parity, float* red, volatile int* abort_flag, int aborted) {
+  if (threadIdx.x == 0) stamp(a, 5);
+  if (EPI != EPI_STORE) {
+    if (!aborted) {
+      if (EPI == EPI_PUSH) {
+        switch (a.world) {
+          case 1: reduce_rows<1, false>(a, parity, red, abort_flag); break;
+          case 2: reduce_rows<2, false>(a, parity, red, abort_flag); break;
+          case 4: reduce_rows<4, false>(a, parity, red, abort_flag); break;
+          default: reduce_rows<8, false>(a, parity, red, abort_flag); break;
+        }
+      } else {
+        int rows_done = 0;
+        switch (a.world) {
+          case 2: rows_done = reduce_rows<2, true>(a, parity, red, abort_flag); break;
+          case 4: rows_done = reduce_rows<4, true>(a, parity, red, abort_flag); break;
+          default: rows_done = reduce_rows<8, true>(a, parity, red, abort_flag); break;
+        }
+        // the finished rows must be visible on every GPU before their count is
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0 && rows_done > 0) {
+          for (int r = 0; r < a.world; ++r)
+            if (r != a.rank)
+              asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a.rowcnt[r] + parity), "r"(static_cast<unsigned int>(rows_done)) : "memory");
+        }
+        // one CTA holds the launch open until the rows owned elsewhere have all arrived here
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+          const int mine = owned_rows(a.M, a.world, a.rank);
+          const unsigned int expect = static_cast<unsigned int>(a.M - mine);
+          unsigned int* cnt = a.rowcnt[a.rank] + parity;
+          const uint64_t t0 = b2::globaltimer_ns();
+          for (uint32_t spin = 0;; ++spin) {
+            unsigned int got;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(cnt) : "memory");
+            if (got >= expect) break;
+            if ((spin & 0xFF) == 0xFF && b2::globaltimer_ns() - t0 > a.timeout_ns) {
+              b2::report_timeout(a.status, B2_WAIT_ROWS);
+              break;
+            }
+          }
+          *reinterpret_cast<volatile unsigned int*>(cnt) = 0;  // next used two launches from now, after every peer has seen this launch end
+        }
+      }
+    }
+    // the last CTA to finish advances the launch parity for the next call
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      stamp(a, 6);
+      __threadfence();
+      const unsigned int prev = atomicAdd(&a.dstate->rowpar_done, 1u);
+      if (prev == gridDim.x - 1) {
+        a.dstate->rowpar_done = 0;
+        a.dstate->rowpar_seq += 1;
+        __threadfence();
+      }
+    }
   }
 }
 
@@ -547,6 +649,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
     } else {
       // ---------------- epilogue warps ----------------
       const int q = warp & 3;  // TMEM lane quadrant this warp may read
+      unsigned char* wbuf = smem + STAGES * C::STAGE_BYTES + 256 + q * STAGING_BYTES_PER_WARP;  // token-row layout only
       b2::pdl_wait();
       if (EPI != EPI_STORE) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
       int u = 0, seg = 0;
@@ -569,7 +672,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-            emit_chunk<SWAP, EPI>(a, v, p_row, tq * BN + c * 32, lane, parity);
+            emit_chunk<BN, SWAP, EPI>(a, v, p_row, tq * BN, c, lane, parity, wbuf);
           }
         } else {
           // This CTA holds only part of the tile's K range.  Every contributor adds its part into the
@@ -609,7 +712,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
               }
 #pragma unroll
               for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(slot + (c * 8 + j) * 128) = make_float4(0.f, 0.f, 0.f, 0.f);
-              emit_chunk<SWAP, EPI>(a, v, p_row, tq * BN + c * 32, lane, parity);
+              emit_chunk<BN, SWAP, EPI>(a, v, p_row, tq * BN, c, lane, parity, wbuf);
             }
           }
         }
@@ -637,63 +740,227 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   }
   if (warp == 1 && has_gemm) b2::tmem_dealloc(tmem_base, C::TMEM_COLS);
 
-  if (threadIdx.x == 0) stamp(a, 5);
-  if (EPI != EPI_STORE) {
-    if (!aborted) {
-      if (EPI == EPI_PUSH) {
-        switch (a.world) {
-          case 1: reduce_rows<1, false>(a, parity, red, abort_flag); break;
-          case 2: reduce_rows<2, false>(a, parity, red, abort_flag); break;
-          case 4: reduce_rows<4, false>(a, parity, red, abort_flag); break;
-          default: reduce_rows<8, false>(a, parity, red, abort_flag); break;
-        }
-      } else {
-        int rows_done = 0;
-        switch (a.world) {
-          case 2: rows_done = reduce_rows<2, true>(a, parity, red, abort_flag); break;
-          case 4: rows_done = reduce_rows<4, true>(a, parity, red, abort_flag); break;
-          default: rows_done = reduce_rows<8, true>(a, parity, red, abort_flag); break;
-        }
-        // the finished rows must be visible on every GPU before their count is
-        __threadfence_system();
-        __syncthreads();
-        if (threadIdx.x == 0 && rows_done > 0) {
-          for (int r = 0; r < a.world; ++r)
-            if (r != a.rank)
-              asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a.rowcnt[r] + parity), "r"(static_cast<unsigned int>(rows_done)) : "memory");
-        }
-        // one CTA holds the launch open until the rows owned elsewhere have all arrived here
-        if (blockIdx.x == 0 && threadIdx.x == 0) {
-          const int mine = owned_rows(a.M, a.world, a.rank);
-          const unsigned int expect = static_cast<unsigned int>(a.M - mine);
-          unsigned int* cnt = a.rowcnt[a.rank] + parity;
-          const uint64_t t0 = b2::globaltimer_ns();
-          for (uint32_t spin = 0;; ++spin) {
-            unsigned int got;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(cnt) : "memory");
-            if (got >= expect) break;
-            if ((spin & 0xFF) == 0xFF && b2::globaltimer_ns() - t0 > a.timeout_ns) {
-              b2::report_timeout(a.status, B2_WAIT_ROWS);
-              break;
-            }
-          }
-          *reinterpret_cast<volatile unsigned int*>(cnt) = 0;  // next used two launches from now, after every peer has seen this launch end
-        }
+  fused_tail<EPI>(a, parity, red, abort_flag, aborted);
+}
+
+// ---------------------------------------------------------------------------
+// Few tokens, few output tiles (decode): one thread-block cluster per 128-feature output tile.
+// The S CTAs of a cluster split the tile's K range; every CTA accumulates its part in tensor memory,
+// then the parts are combined through distributed shared memory: the accumulator's 4-column groups are
+// dealt round-robin to the CTAs of the cluster, each CTA receives the other CTAs' parts of its groups
+// in its own shared memory, sums them after one cluster barrier, and writes its share of the output
+// as whole 256-byte token rows.  No global-memory round trip and no atomics on the critical path.
+// Feature-lane layout only (weights on the 128-row MMA side), one token tile (M <= BN).
+// ---------------------------------------------------------------------------
+template <int BN>
+struct CfgCluster {
+  static constexpr uint32_t P_BYTES = BM * BK * 2;
+  static constexpr uint32_t Q_BYTES = BN * BK * 2;
+  static constexpr uint32_t STAGE_BYTES = P_BYTES + Q_BYTES;
+  static constexpr int GROUPS = BN / 4;                                 // 4-column groups of the accumulator
+  static constexpr uint32_t RED_BYTES = (GROUPS + 8) * BM * 16;         // [source CTA][local group][feature][4] fp32
+  static constexpr uint32_t OUT_BYTES = BN * BM * 2;                    // [token][feature] bf16 staging of the output
+  static constexpr int STAGES_RAW = (200704 - RED_BYTES - OUT_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + RED_BYTES + OUT_BYTES;
+  static_assert(STAGES >= 3, "too little shared memory left for the operand pipeline");
+  static_assert(SMEM_BYTES <= 232448, "more shared memory than an SM has");
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const GemmArgs a) {
+  using C = CfgCluster<BN>;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw_addr = b2::smem_u32(smem_raw);
+  unsigned char* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  const uint32_t smem_base = b2::smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES);
+  const uint32_t bar_full = b2::smem_u32(bars);
+  const uint32_t bar_empty = bar_full + STAGES * 8;
+  const uint32_t bar_tfull = bar_empty + STAGES * 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  unsigned char* red_buf = smem + STAGES * C::STAGE_BYTES + 256;
+  unsigned char* out_buf = red_buf + C::RED_BYTES;
+  __shared__ float red[NUM_THREADS / 32];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = static_cast<int>(b2::cluster_nctarank());
+  const int crank = static_cast<int>(b2::cluster_ctarank());
+  const int tile = blockIdx.x / S;  // the output tile of this cluster: features [tile * 128, +128)
+  const int KB = a.kblocks;
+  const int kb_base = KB / S, kb_rem = KB % S;
+  const int kb0 = crank * kb_base + min(crank, kb_rem);
+  const int n_units = kb_base + (crank < kb_rem ? 1 : 0);
+  const int GL = (C::GROUPS + S - 1) / S;  // most groups any CTA of the cluster owns
+
+  if (threadIdx.x == 0) {
+    stamp(a, 7);
+    b2::tma_prefetch_desc(&tmP);
+    b2::tma_prefetch_desc(&tmQ);
+    for (int s = 0; s < STAGES; ++s) {
+      b2::mbar_init(bar_full + s * 8, 1);
+      b2::mbar_init(bar_empty + s * 8, 1);
+    }
+    b2::mbar_init(bar_tfull, 1);
+    *abort_flag = 0;
+    b2::mbar_fence_init();
+  }
+  if (warp == 1) {
+    b2::tmem_alloc(b2::smem_u32(tmem_slot), C::TMEM_COLS);
+    b2::tmem_relinquish();
+  }
+  b2::tc_fence_before();
+  __syncthreads();
+  b2::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) b2::pdl_launch_dependents();
+  if (threadIdx.x == 0) stamp(a, 0);
+  unsigned int parity = 0;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const int pre = n_units < STAGES ? n_units : STAGES;
+      for (int i = 0; i < pre; ++i) {  // weights do not depend on earlier kernels
+        const uint32_t fb = bar_full + i * 8;
+        b2::mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
+        b2::tma_load_2d(smem_base + i * C::STAGE_BYTES, &tmP, fb, (kb0 + i) * BK, tile * BM, b2::kEvictFirst);
+      }
+      b2::pdl_wait();
+      stamp(a, 3);
+      for (int i = 0; i < pre; ++i)
+        b2::tma_load_2d(smem_base + i * C::STAGE_BYTES + C::P_BYTES, &tmQ, bar_full + i * 8, (kb0 + i) * BK, 0, b2::kEvictLast);
+      int stage = pre == STAGES ? 0 : pre;
+      uint32_t phase = pre == STAGES ? 1 : 0;
+      for (int i = pre; i < n_units; ++i) {
+        if (!b2::mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_SMEM_EMPTY)) break;
+        const uint32_t fb = bar_full + stage * 8;
+        b2::mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
+        const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
+        b2::tma_load_2d(dst, &tmP, fb, (kb0 + i) * BK, tile * BM, b2::kEvictFirst);
+        b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, (kb0 + i) * BK, 0, b2::kEvictLast);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
-    // the last CTA to finish advances the launch parity for the next call
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      stamp(a, 6);
-      __threadfence();
-      const unsigned int prev = atomicAdd(&a.dstate->rowpar_done, 1u);
-      if (prev == gridDim.x - 1) {
-        a.dstate->rowpar_done = 0;
-        a.dstate->rowpar_seq += 1;
-        __threadfence();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = b2::umma_idesc_bf16(BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int i = 0; i < n_units; ++i) {
+        if (!b2::mbar_wait(bar_full + stage * 8, phase, abort_flag, PIPE_LIMIT_NS, B2_WAIT_SMEM_FULL)) { ok = false; break; }
+        if (i == 0) stamp(a, 1);
+        b2::tc_fence_after();
+        const uint32_t sp = smem_base + stage * C::STAGE_BYTES;
+        const uint64_t dp = b2::umma_smem_desc(sp);
+        const uint64_t dq = b2::umma_smem_desc(sp + C::P_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) b2::umma_bf16(tmem_base, dp + 2 * k, dq + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        b2::umma_commit(bar_empty + stage * 8);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+      if (ok) b2::umma_commit(bar_tfull);
+      stamp(a, 2);
+    }
+  } else {
+    // ---------------- epilogue, first half: hand every group of the accumulator to the CTA that owns it ----------------
+    const int q = warp & 3;
+    const int f = q * 32 + lane;  // feature row of the tile this thread holds
+    b2::pdl_wait();
+    if (EPI != EPI_STORE) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
+    if (b2::mbar_wait(bar_tfull, 0, abort_flag, PIPE_LIMIT_NS, B2_WAIT_TMEM_FULL)) {
+      b2::tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t red_local = b2::smem_u32(red_buf);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        b2::tmem_ld_32x32(taddr + c * 32, r);
+        b2::tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int g = c * 8 + j, owner = g % S, gl = g / S;
+          const uint32_t local = red_local + ((crank * GL + gl) * BM + f) * 16;
+          b2::st_cluster_v4(b2::map_to_cta(local, owner), __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                            __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        }
       }
     }
   }
+
+  // ---- every thread of the cluster meets: all parts have been delivered ----
+  __syncwarp();
+  b2::cluster_arrive();
+  b2::cluster_wait();
+
+  if (warp >= 2 && !*abort_flag) {
+    // ---------------- epilogue, second half: sum the S parts of the owned groups, stage, store whole token rows ----------------
+    const int q = warp & 3;
+    const int f = q * 32 + lane;
+    const int feature = tile * BM + f;
+    float bias = 0.f;
+    if (a.bias != nullptr && feature < a.N) bias = __uint_as_float(static_cast<uint32_t>(a.bias[feature]) << 16);
+    uint16_t* out16 = reinterpret_cast<uint16_t*>(out_buf);
+    int owned = 0;
+    for (int gl = 0; gl < GL; ++gl) {
+      const int g = gl * S + crank;
+      if (g >= C::GROUPS) break;
+      float4 sum = make_float4(bias, bias, bias, bias);
+      for (int src = 0; src < S; ++src) {
+        const float4 t = *reinterpret_cast<const float4*>(red_buf + ((src * GL + gl) * BM + f) * 16);
+        sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+      }
+      const uint32_t lo = b2::pack_bf16(sum.x, sum.y), hi = b2::pack_bf16(sum.z, sum.w);
+      out16[(gl * 4 + 0) * BM + f] = static_cast<uint16_t>(lo & 0xFFFF);
+      out16[(gl * 4 + 1) * BM + f] = static_cast<uint16_t>(lo >> 16);
+      out16[(gl * 4 + 2) * BM + f] = static_cast<uint16_t>(hi & 0xFFFF);
+      out16[(gl * 4 + 3) * BM + f] = static_cast<uint16_t>(hi >> 16);
+      owned = gl + 1;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+    // rows of out_buf: local token index lt = gl * 4 + j  <->  token (gl * S + crank) * 4 + j; 16 pieces of 16 bytes per row
+    const int et = threadIdx.x - 64;
+    for (int idx = et; idx < owned * 4 * 16; idx += 128) {
+      const int lt = idx >> 4, piece = idx & 15;
+      const int token = (((lt >> 2) * S + crank) << 2) + (lt & 3);
+      const int feat = tile * BM + piece * 8;
+      if (token < a.M && feat < a.N) {
+        uint4 w = *reinterpret_cast<const uint4*>(out_buf + lt * (BM * 2) + piece * 16);
+        if (EPI == EPI_STORE) {
+          *reinterpret_cast<uint4*>(a.C + token * a.ldc + feat) = w;
+        } else {
+          w.x = b2::scrub_sentinel(w.x); w.y = b2::scrub_sentinel(w.y);
+          w.z = b2::scrub_sentinel(w.z); w.w = b2::scrub_sentinel(w.w);
+          const size_t off = parity * a.parity_stride + a.rank * a.slot_stride + (static_cast<size_t>(token) * a.N + feat) * 2;
+#pragma unroll
+          for (int r = 0; r < B2_MAX_WORLD; ++r)
+            if (r < a.world) *reinterpret_cast<uint4*>(a.inbox[r] + off) = w;
+        }
+      }
+    }
+    if (warp == 2 && lane == 0) stamp(a, 4);
+  }
+
+  // ---- all roles meet; tensor memory goes back ------------------------------
+  b2::pdl_wait();
+  if (EPI != EPI_STORE) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
+  __syncwarp();
+  b2::tc_fence_before();
+  __syncthreads();
+  b2::tc_fence_after();
+  const int aborted = *abort_flag;
+  if (aborted) {
+    for (int i = 0; i < 100; ++i) __nanosleep(2000);
+    if (threadIdx.x == 0) b2::report_timeout(a.status, aborted);
+  }
+  if (warp == 1) b2::tmem_dealloc(tmem_base, C::TMEM_COLS);
+  fused_tail<EPI>(a, parity, red, abort_flag, aborted);
 }
 
 // ---------------------------------------------------------------------------
@@ -704,12 +971,78 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 template <int BN, bool SWAP, int EPI>
 int launch_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmArgs& args, int grid, cudaStream_t stream) {
   static bool configured = false;
+  constexpr uint32_t smem_bytes = SWAP ? Cfg<BN>::SMEM_BYTES : Cfg<BN>::SMEM_BYTES_ROWS;
+  static_assert(smem_bytes <= 232448, "more shared memory than an SM has");
   if (!configured) {
-    B2_CUDA(cudaFuncSetAttribute(gemm_kernel<BN, SWAP, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
+    B2_CUDA(cudaFuncSetAttribute(gemm_kernel<BN, SWAP, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     configured = true;
   }
-  B2_CUDA(b2_launch(gemm_kernel<BN, SWAP, EPI>, dim3(grid), dim3(NUM_THREADS), Cfg<BN>::SMEM_BYTES, stream, tmP, tmQ, args));
+  B2_CUDA(b2_launch(gemm_kernel<BN, SWAP, EPI>, dim3(grid), dim3(NUM_THREADS), smem_bytes, stream, tmP, tmQ, args));
   return B2_OK;
+}
+
+template <int BN, int EPI>
+int launch_cluster_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmArgs& args, int tiles, int S, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    B2_CUDA(cudaFuncSetAttribute(gemm_cluster_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, CfgCluster<BN>::SMEM_BYTES));
+    configured = true;
+  }
+  B2_CUDA(b2_launch_cluster(gemm_cluster_kernel<BN, EPI>, dim3(tiles * S), dim3(NUM_THREADS), CfgCluster<BN>::SMEM_BYTES, stream,
+                            static_cast<unsigned>(S), tmP, tmQ, args));
+  return B2_OK;
+}
+
+// How many clusters of S CTAs of the cluster kernel can be resident at once (cached per BN and S).
+template <int BN, int EPI>
+int max_resident_clusters(int S) {
+  static int cache[9] = {0, -1, -1, -1, -1, -1, -1, -1, -1};
+  if (S < 1 || S > 8) return 0;
+  if (cache[S] >= 0) return cache[S];
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_cluster_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, CfgCluster<BN>::SMEM_BYTES) != cudaSuccess) return 0;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(S * 64);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = CfgCluster<BN>::SMEM_BYTES;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_cluster_kernel<BN, EPI>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  cache[S] = n;
+  return n;
+}
+
+bool cluster_path_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("B2_CLUSTER");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
+// Picks the K split S of the cluster kernel for `tiles` output tiles of `kblocks` K blocks: the largest S that
+// keeps every cluster resident in one wave and leaves each CTA at least two K blocks.  0 = use the stream-K kernel.
+template <int BN, int EPI>
+int pick_cluster_split(int tiles, int kblocks, int num_sms) {
+  if (!cluster_path_enabled() || tiles > num_sms) return 0;
+  for (int S = 8; S >= 1; --S) {
+    if (S > 1 && kblocks < 2 * S) continue;
+    if (tiles * S > num_sms) continue;
+    if (max_resident_clusters<BN, EPI>(S) >= tiles) return S;
+  }
+  return 0;
 }
 
 template <int EPI>
@@ -763,6 +1096,15 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
   if (rc != B2_OK) return rc;
 
   if constexpr (EPI != EPI_PUSH2) {
+    if (swap && args.tilesQ == 1 && bn <= 64) {  // up to 64 tokens: the decode sizes
+      const int S = bn == 32 ? pick_cluster_split<32, EPI>(args.tilesP, args.kblocks, ctx->num_sms)
+                             : pick_cluster_split<64, EPI>(args.tilesP, args.kblocks, ctx->num_sms);
+      if (S > 0) {
+        args.gemm_ctas = args.tilesP * S;
+        if (bn == 32) return launch_cluster_inst<32, EPI>(tmP, tmQ, args, args.tilesP, S, stream);
+        return launch_cluster_inst<64, EPI>(tmP, tmQ, args, args.tilesP, S, stream);
+      }
+    }
     if (swap) {
       switch (bn) {
         case 32: return launch_inst<32, true, EPI>(tmP, tmQ, args, grid, stream);
@@ -906,7 +1248,7 @@ int b2_rowpar_fused_twoshot(b2_ctx* ctx, const void* A, int64_t lda, const void*
   GemmArgs args{};
   args.bias = (ctx->cfg.rank == 0) ? static_cast<const uint16_t*>(bias) : nullptr;
   args.rows_per_rank = owned_rows(M, world, 0);
-  const size_t max_rows = ((static_cast<size_t>(ctx->cfg.max_tokens) + 127) / 128 + world - 1) / world * 128;
+  const size_t max_rows = ((static_cast<size_t>(ctx->cfg.max_tokens) + OWN_ROWS - 1) / OWN_ROWS + world - 1) / world * OWN_ROWS;
   args.slot_stride = max_rows * ctx->cfg.hidden * 2;
   args.parity_stride = args.slot_stride * world;
   for (int r = 0; r < world; ++r) {

@@ -46,7 +46,10 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> 
     return out.view(*lead, N)
 
 
-TWO_SHOT_MIN_TOKENS = 257  # from this many tokens on (and tensor-parallel size >= 2) the two-shot kernel is used
+def _two_shot_min_tokens(world: int) -> int:
+    """From this many tokens on the two-shot kernel is used.  One-shot pushes (world-1) copies of the partial,
+    two-shot 2 (world-1)/world: the same at world 2, 4.6x less at world 8."""
+    return 257 if world <= 2 else 128
 
 
 def rowpar_fused(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, residual: torch.Tensor | None,
@@ -56,7 +59,7 @@ def rowpar_fused(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, re
 
     For many tokens at tensor-parallel size >= 2 the two-shot kernel runs: `normed` is then a view of a
     buffer owned by the runtime (valid until the next such call) and `new_residual` holds only the rows
-    this rank owns (128-row blocks rank, rank + world, ...); the next fused call reads exactly those rows."""
+    this rank owns (16-row blocks rank, rank + world, ...); the next fused call reads exactly those rows."""
     x2 = _as2d(_bf16_rows(x, "row-parallel input"))
     if x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
         x2 = x2.contiguous()
@@ -70,7 +73,7 @@ def rowpar_fused(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, re
             residual = residual.contiguous()
         res_out = torch.empty_like(residual)
     args_tail = (residual.data_ptr() if norm_w is not None else None, norm_w.data_ptr() if norm_w is not None else None, float(eps))
-    if rt.world >= 2 and M >= TWO_SHOT_MIN_TOKENS and N == rt.hidden and M <= rt.max_tokens:
+    if rt.world >= 2 and M >= _two_shot_min_tokens(rt.world) and N == rt.hidden and M <= rt.max_tokens:
         ptr = C.c_void_p()
         _abi.check(_lib.b2_rowpar_fused_twoshot(rt.ctx, x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0),
                                                 bias.data_ptr() if bias is not None else None, M, N, Kr, *args_tail, C.byref(ptr),
