@@ -109,6 +109,16 @@ int64_t b2_launch_count(void);
 int b2_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias,
             void* C, int64_t ldc, int M, int N, int K, void* stream);
 
+/* ---- gate_up projection fused with SiLU(gate) * up: replaces the pair
+ *      MergedColumnParallelLinear.forward + SiluAndMul.forward in Qwen3MLP
+ *      (nanovllm/models/qwen3.py:113-116; nanovllm/layers/activation.py:8-11) --
+ * W_pairs [2 I, K] holds the rank's gate and up rows interleaved: row 2 j is
+ * gate row j, row 2 j + 1 is up row j.  out[M, I] = silu(A gate_j^T) * (A up_j^T)
+ * with the reference's roundings (both products to bf16, the activation to
+ * bf16, then the product).  The [M, 2 I] intermediate never reaches HBM. */
+int b2_gemm_silu_mul(b2_ctx* ctx, const void* A, int64_t lda, const void* W_pairs, int64_t ldw, void* out, int64_t ldo,
+                     int M, int I, int K, void* stream);
+
 /* ---- the same GEMM for callers that cannot allocate device memory.  It has
  *      no counterpart in the reference. ----------------------------------------
  * b2_gemm needs a context, and creating one calls cudaMalloc.  Some users of

@@ -58,6 +58,7 @@ struct GemmArgs {
   uint16_t* C;
   int64_t ldc;
   const uint16_t* bias;
+  int silu_pairs;  // 1: features come in (gate, up) pairs; store silu(gate) * up, one value per pair, at column feature / 2
   // stream-K combine
   float* ws;
   int* counters;
@@ -74,8 +75,7 @@ struct GemmArgs {
   B2DeviceState* dstate;
   uint64_t timeout_ns;
   // EPI_PUSH2 (inbox / parity_stride / slot_stride then describe the row-owner inbox)
-  unsigned char* outbuf[B2_MAX_WORLD];   // every rank's [max_tokens][hidden] output buffer
-  unsigned int* rowcnt[B2_MAX_WORLD];    // every rank's [2] rows-received counters
+  size_t out_off, rowcnt_off;  // from inbox[r]: that rank's [max_tokens][hidden] output buffer and its [2] rows-received counters
   int rows_per_rank;
   unsigned long long* trace;  // optional [CTA][8][2] (SM clock, global ns) phase stamps; null = off
 };
@@ -86,7 +86,8 @@ struct Cfg {
   static constexpr uint32_t Q_BYTES = BN * BK * 2;
   static constexpr uint32_t STAGE_BYTES = P_BYTES + Q_BYTES;
   static constexpr int STAGES = (196608 / STAGE_BYTES) > 8 ? 8 : (196608 / STAGE_BYTES);
-  static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int ACC = BN <= 128 ? 4 : 2;  // accumulators in tensor memory (512 columns in all)
+  static constexpr uint32_t TMEM_COLS = ACC * BN;
   static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static constexpr uint32_t SMEM_BYTES_ROWS = SMEM_BYTES + 4 * 8192 /*epilogue staging of the token-row layout*/;
 };
@@ -123,6 +124,30 @@ __device__ __forceinline__ void unit_at(const Work& w, int i, int& tile, int& kb
     kb = u - tile * w.KB;
   }
 }
+// Walks the units one by one without dividing: the TMA producer is a single thread whose instruction
+// stream competes with an epilogue warp for issue slots, so its per-K-block arithmetic has to stay short.
+struct Cursor {
+  int tile, kb, tp, tq;
+};
+__device__ __forceinline__ Cursor cursor_begin(const Work& w, int tilesQ) {
+  Cursor c;
+  unit_at(w, 0, c.tile, c.kb);
+  c.tp = c.tile / tilesQ;
+  c.tq = c.tile - c.tp * tilesQ;
+  return c;
+}
+__device__ __forceinline__ void cursor_next(const Work& w, int tilesQ, Cursor& c) {
+  if (++c.kb == w.KB) {
+    c.kb = 0;
+    const int step = w.rr ? w.G : 1;
+    c.tile += step;
+    c.tq += step;
+    while (c.tq >= tilesQ) {  // at most a few turns: step <= G, and tilesQ is 1 whenever G is large relative to it
+      c.tq -= tilesQ;
+      ++c.tp;
+    }
+  }
+}
 __device__ __forceinline__ bool next_seg(const Work& w, int& i, Seg& s) {
   if (i >= w.n_units) return false;
   int tile, kb;
@@ -156,6 +181,17 @@ __host__ __device__ inline int owned_rows(int M, int world, int rank) {
 // (row of the P tile) q*32 + lane and columns c*32 .. c*32+31 (rows of the Q
 // tile).
 // ---------------------------------------------------------------------------
+// silu(gate) * up on bf16-rounded inputs, with the reference's roundings (nanovllm/layers/activation.py:8-11, eager):
+// the activation is rounded to bf16 before the product, the product once more by the caller's pack
+__device__ __forceinline__ float silu_mul(float gate, float up) {
+  return b2::bf16_round(gate / (1.0f + expf(-gate))) * up;
+}
+// 8 bf16 = 4 (gate, up) pairs -> 4 bf16
+__device__ __forceinline__ uint2 silu_mul_pairs(const uint4& w) {
+  return make_uint2(b2::pack_bf16(silu_mul(b2::bf16_lo(w.x), b2::bf16_hi(w.x)), silu_mul(b2::bf16_lo(w.y), b2::bf16_hi(w.y))),
+                    b2::pack_bf16(silu_mul(b2::bf16_lo(w.z), b2::bf16_hi(w.z)), silu_mul(b2::bf16_lo(w.w), b2::bf16_hi(w.w))));
+}
+
 // NC columns (tokens token0 ..) of one feature per lane, features = consecutive lanes.
 // Lanes 2i and 2i+1 hold features f and f+1 of the same tokens.  They swap
 // halves so that each lane stores a packed (f, f+1) pair: the even lane for
@@ -178,7 +214,12 @@ __device__ __forceinline__ void emit_feature_lanes(const GemmArgs& a, float (&v)
     uint32_t w = odd ? b2::pack_bf16(recv, v[j + 1]) : b2::pack_bf16(v[j], recv);
     if (token < a.M && fbase < a.N) {
       if (EPI == EPI_STORE) {
-        *reinterpret_cast<uint32_t*>(a.C + token * a.ldc + fbase) = w;
+        if (a.silu_pairs) {  // w = (gate, up) of feature pair fbase / 2
+          const float act = silu_mul(b2::bf16_lo(w), b2::bf16_hi(w));
+          a.C[token * a.ldc + (fbase >> 1)] = static_cast<uint16_t>(b2::pack_bf16(act, 0.f) & 0xFFFF);
+        } else {
+          *reinterpret_cast<uint32_t*>(a.C + token * a.ldc + fbase) = w;
+        }
       } else {
         w = b2::scrub_sentinel(w);
         const size_t off = parity * a.parity_stride + a.rank * a.slot_stride +
@@ -235,7 +276,8 @@ __device__ __forceinline__ void flush_rows(const GemmArgs& a, unsigned char* wbu
     if (piece < npieces && token < a.M && feature < a.N) {
       const uint4 w = *reinterpret_cast<const uint4*>(wbuf + row * STAGE_ROW_BYTES + ((piece ^ (row & 15)) << 4));
       if (EPI == EPI_STORE) {
-        *reinterpret_cast<uint4*>(a.C + token * a.ldc + feature) = w;
+        if (a.silu_pairs) *reinterpret_cast<uint2*>(a.C + token * a.ldc + (feature >> 1)) = silu_mul_pairs(w);
+        else *reinterpret_cast<uint4*>(a.C + token * a.ldc + feature) = w;
       } else if (EPI == EPI_PUSH2) {
         int lrow;
         const int owner = owner_of(token, a.world, lrow);
@@ -377,7 +419,7 @@ __device__ __forceinline__ int reduce_rows(const GemmArgs& a, unsigned int parit
             if (TWO) {
 #pragma unroll
               for (int r = 0; r < B2_MAX_WORLD; ++r)
-                if (r < a.world) *reinterpret_cast<uint4*>(a.outbuf[r] + (out_off + v * 8) * 2) = y;
+                if (r < a.world) *reinterpret_cast<uint4*>(a.inbox[r] + a.out_off + (out_off + v * 8) * 2) = y;
             } else {
               *reinterpret_cast<uint4*>(a.normed_out + out_off + v * 8) = y;
             }
@@ -415,7 +457,7 @@ __device__ __forceinline__ int reduce_rows(const GemmArgs& a, unsigned int parit
         if (TWO) {
 #pragma unroll
           for (int r = 0; r < B2_MAX_WORLD; ++r)
-            if (r < a.world) *reinterpret_cast<uint4*>(a.outbuf[r] + (out_off + v * 8) * 2) = y;
+            if (r < a.world) *reinterpret_cast<uint4*>(a.inbox[r] + a.out_off + (out_off + v * 8) * 2) = y;
         } else {
           *reinterpret_cast<uint4*>(a.normed_out + out_off + v * 8) = y;
         }
@@ -460,13 +502,13 @@ __device__ __forceinline__ void fused_tail(const GemmArgs& a, unsigned int parit
         if (threadIdx.x == 0 && rows_done > 0) {
           for (int r = 0; r < a.world; ++r)
             if (r != a.rank)
-              asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a.rowcnt[r] + parity), "r"(static_cast<unsigned int>(rows_done)) : "memory");
+              asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(reinterpret_cast<unsigned int*>(a.inbox[r] + a.rowcnt_off) + parity), "r"(static_cast<unsigned int>(rows_done)) : "memory");
         }
         // one CTA holds the launch open until the rows owned elsewhere have all arrived here
         if (blockIdx.x == 0 && threadIdx.x == 0) {
           const int mine = owned_rows(a.M, a.world, a.rank);
           const unsigned int expect = static_cast<unsigned int>(a.M - mine);
-          unsigned int* cnt = a.rowcnt[a.rank] + parity;
+          unsigned int* cnt = reinterpret_cast<unsigned int*>(a.inbox[a.rank] + a.rowcnt_off) + parity;
           const uint64_t t0 = b2::globaltimer_ns();
           for (uint32_t spin = 0;; ++spin) {
             unsigned int got;
@@ -512,8 +554,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   const uint32_t bar_full = b2::smem_u32(bars);
   const uint32_t bar_empty = bar_full + STAGES * 8;
   const uint32_t bar_tfull = bar_empty + STAGES * 8;
-  const uint32_t bar_tempty = bar_tfull + 2 * 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  constexpr int ACC = C::ACC;
+  const uint32_t bar_tempty = bar_tfull + ACC * 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * ACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   __shared__ float red[NUM_THREADS / 32];
 
@@ -544,7 +587,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
       b2::mbar_init(bar_full + s * 8, 1);
       b2::mbar_init(bar_empty + s * 8, 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < ACC; ++i) {
       b2::mbar_init(bar_tfull + i * 8, 1);
       b2::mbar_init(bar_tempty + i * 8, 4);
     }
@@ -574,39 +617,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
         const int pre = n_units < STAGES ? n_units : STAGES;
         // The weight tiles of the first stages depend on no earlier kernel: fetch them before the
         // dependency wait, so that they are in flight (or landed) when the activations become valid.
+        Cursor cw = cursor_begin(work, a.tilesQ);
         for (int i = 0; i < pre; ++i) {
-          int tile, kb;
-          unit_at(work, i, tile, kb);
-          const int tp = tile / a.tilesQ, tq = tile - tp * a.tilesQ;
           const uint32_t fb = bar_full + i * 8;
           b2::mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
           const uint32_t dst = smem_base + i * C::STAGE_BYTES;
-          if (SWAP) b2::tma_load_2d(dst, &tmP, fb, kb * BK, tp * BM, polP);
-          else b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, kb * BK, tq * BN, polQ);
+          if (SWAP) b2::tma_load_2d(dst, &tmP, fb, cw.kb * BK, cw.tp * BM, polP);
+          else b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, cw.kb * BK, cw.tq * BN, polQ);
+          cursor_next(work, a.tilesQ, cw);
         }
         b2::pdl_wait();
         stamp(a, 3);
+        Cursor cx = cursor_begin(work, a.tilesQ);
         for (int i = 0; i < pre; ++i) {
-          int tile, kb;
-          unit_at(work, i, tile, kb);
-          const int tp = tile / a.tilesQ, tq = tile - tp * a.tilesQ;
           const uint32_t fb = bar_full + i * 8;
           const uint32_t dst = smem_base + i * C::STAGE_BYTES;
-          if (SWAP) b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, kb * BK, tq * BN, polQ);
-          else b2::tma_load_2d(dst, &tmP, fb, kb * BK, tp * BM, polP);
+          if (SWAP) b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, cx.kb * BK, cx.tq * BN, polQ);
+          else b2::tma_load_2d(dst, &tmP, fb, cx.kb * BK, cx.tp * BM, polP);
+          cursor_next(work, a.tilesQ, cx);
         }
         int stage = pre == STAGES ? 0 : pre;
         uint32_t phase = pre == STAGES ? 1 : 0;
-        for (int i = pre; i < n_units; ++i) {
-          int tile, kb;
-          unit_at(work, i, tile, kb);
-          const int tp = tile / a.tilesQ, tq = tile - tp * a.tilesQ;
+        for (int i = pre; i < n_units; ++i) {  // cx now stands at unit `pre`
           if (!b2::mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_SMEM_EMPTY)) break;
           const uint32_t fb = bar_full + stage * 8;
           b2::mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
           const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
-          b2::tma_load_2d(dst, &tmP, fb, kb * BK, tp * BM, polP);
-          b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, kb * BK, tq * BN, polQ);
+          b2::tma_load_2d(dst, &tmP, fb, cx.kb * BK, cx.tp * BM, polP);
+          b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, cx.kb * BK, cx.tq * BN, polQ);
+          cursor_next(work, a.tilesQ, cx);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -620,8 +659,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
         Seg s;
         bool ok = true;
         while (ok && next_seg(work, u, s)) {
-          const int acc = seg & 1;
-          const uint32_t use = static_cast<uint32_t>(seg >> 1);  // how often this accumulator was used before
+          const int acc = seg % ACC;
+          const uint32_t use = static_cast<uint32_t>(seg / ACC);  // how often this accumulator was used before
           if (!b2::mbar_wait(bar_tempty + acc * 8, (use & 1) ^ 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_TMEM_EMPTY)) break;
           b2::tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * BN;
@@ -655,8 +694,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
       int u = 0, seg = 0;
       Seg s;
       while (next_seg(work, u, s)) {
-        const int acc = seg & 1;
-        const uint32_t use = static_cast<uint32_t>(seg >> 1);
+        const int acc = seg % ACC;
+        const uint32_t use = static_cast<uint32_t>(seg / ACC);
         if (!b2::mbar_wait(bar_tfull + acc * 8, use & 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_TMEM_FULL)) break;
         b2::tc_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
@@ -933,7 +972,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
       if (token < a.M && feat < a.N) {
         uint4 w = *reinterpret_cast<const uint4*>(out_buf + lt * (BM * 2) + piece * 16);
         if (EPI == EPI_STORE) {
-          *reinterpret_cast<uint4*>(a.C + token * a.ldc + feat) = w;
+          if (a.silu_pairs) *reinterpret_cast<uint2*>(a.C + token * a.ldc + (feat >> 1)) = silu_mul_pairs(w);
+          else *reinterpret_cast<uint4*>(a.C + token * a.ldc + feat) = w;
         } else {
           w.x = b2::scrub_sentinel(w.x); w.y = b2::scrub_sentinel(w.y);
           w.z = b2::scrub_sentinel(w.z); w.w = b2::scrub_sentinel(w.w);
@@ -1084,6 +1124,7 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
   g = std::min<int64_t>(g, U);
   args.gemm_ctas = static_cast<int>(g);
   args.round_robin = (!swap && tiles >= 4 * g) ? 1 : 0;
+
   const int grid = (EPI == EPI_PUSH2) ? ctx->num_sms : std::max(args.gemm_ctas, std::min(min_grid, ctx->num_sms));
 
   CUtensorMap tmP, tmQ;
@@ -1228,6 +1269,21 @@ int b2_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw,
   return launch_gemm<EPI_STORE>(ctx, A, lda, W, ldw, M, N, K, args, 0, static_cast<cudaStream_t>(stream));
 }
 
+int b2_gemm_silu_mul(b2_ctx* ctx, const void* A, int64_t lda, const void* W_pairs, int64_t ldw, void* out, int64_t ldo, int M, int I, int K,
+                     void* stream) {
+  if (ctx == nullptr) return B2_ERR_ARG;
+  if (I <= 0 || I % 8 != 0) return B2_ERR_ARG;
+  int rc = check_operands(A, lda, W_pairs, ldw, M, 2 * I, K);
+  if (rc != B2_OK) return rc;
+  if (M == 0) return B2_OK;
+  if (!out || !aligned16(out) || ldo % 8 != 0 || ldo < I) return B2_ERR_ARG;
+  GemmArgs args{};
+  args.C = static_cast<uint16_t*>(out);
+  args.ldc = ldo;
+  args.silu_pairs = 1;
+  return launch_gemm<EPI_STORE>(ctx, A, lda, W_pairs, ldw, M, 2 * I, K, args, 0, static_cast<cudaStream_t>(stream));
+}
+
 int b2_rowpar_fused_twoshot(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias, int M, int N, int Kr,
                             const void* residual_in, const void* norm_w, float eps, void** normed_out, void* residual_out, void* stream) {
   if (ctx == nullptr || normed_out == nullptr) return B2_ERR_ARG;
@@ -1253,9 +1309,9 @@ int b2_rowpar_fused_twoshot(b2_ctx* ctx, const void* A, int64_t lda, const void*
   args.parity_stride = args.slot_stride * world;
   for (int r = 0; r < world; ++r) {
     args.inbox[r] = ctx->peer[r] + ctx->off_inbox2;
-    args.outbuf[r] = ctx->peer[r] + ctx->off_out;
-    args.rowcnt[r] = reinterpret_cast<unsigned int*>(ctx->peer[r] + ctx->off_rowcnt);
   }
+  args.out_off = ctx->off_out - ctx->off_inbox2;
+  args.rowcnt_off = ctx->off_rowcnt - ctx->off_inbox2;
   args.world = world;
   args.rank = ctx->cfg.rank;
   args.residual_in = static_cast<const uint16_t*>(residual_in);

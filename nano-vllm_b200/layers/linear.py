@@ -94,6 +94,24 @@ class MergedColumnParallelLinear(ColumnParallelLinear):
         offset = sum(self.output_sizes[:loaded_shard_id]) // self.tp_size
         size = self.output_sizes[loaded_shard_id] // self.tp_size
         param.data.narrow(self.tp_dim, offset, size).copy_(self._shard_of(loaded_weight, self.tp_dim))
+        self._pairs = None
+
+    _pairs: torch.Tensor | None = None
+
+    def paired_weight(self) -> torch.Tensor:
+        """The local weight with the two halves' rows interleaved (row 2j = first half's row j, row 2j+1 = second
+        half's row j): the layout ops.gemm_silu_mul reads.  Built once from `weight` (which keeps the reference's
+        [first half ; second half] layout) the first time it is asked for; costs a second copy of the weight."""
+        if self._pairs is None:
+            assert len(self.output_sizes) == 2 and self.output_sizes[0] == self.output_sizes[1] and self.bias is None
+            half = self.weight.shape[0] // 2
+            w = self.weight.data
+            self._pairs = torch.stack((w[:half], w[half:]), dim=1).reshape(2 * half, w.shape[1]).contiguous()
+        return self._pairs
+
+    def forward_silu_mul(self, x: torch.Tensor) -> torch.Tensor:
+        """SiLU(first half) * second half of forward(x), in the GEMM's epilogue."""
+        return ops.gemm_silu_mul(x, self.paired_weight())
 
 
 class QKVParallelLinear(ColumnParallelLinear):

@@ -10,7 +10,7 @@ same tensors.  The data flow differs in where the norms run:
   h = attn(h)          # o_proj + NCCL      qkv GEMM; q/k-norm + RoPE + KV scatter (1 kernel);
   h, res = post_attention_layernorm(h,res)  attention (library); o_proj GEMM + cross-GPU sum
   h = mlp(h)           # down_proj + NCCL     + residual + post_attention_layernorm (1 kernel);
-                                            gate_up GEMM; SiLU*mul; down_proj GEMM + cross-GPU
+                                            gate_up GEMM with SiLU*mul in its epilogue; down_proj GEMM + cross-GPU
                                               sum + residual + NEXT layer's input_layernorm
                                               (or the final norm) (1 kernel)
 """
@@ -82,7 +82,8 @@ class Qwen3MLP(nn.Module):
         self.act_fn = SiluAndMul()
 
     def activation(self, x: torch.Tensor) -> torch.Tensor:
-        return self.act_fn(self.gate_up_proj(x))
+        """act_fn(gate_up_proj(x)) in one launch: the SiLU * mul runs in the GEMM's epilogue."""
+        return self.gate_up_proj.forward_silu_mul(x)
 
     def forward(self, x):
         return self.down_proj(self.activation(x))

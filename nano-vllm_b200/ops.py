@@ -46,6 +46,21 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> 
     return out.view(*lead, N)
 
 
+def gemm_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor) -> torch.Tensor:
+    """silu(x @ gate^T) * (x @ up^T) where w_pairs interleaves gate and up rows (gate_0, up_0, gate_1, ...)."""
+    lead = x.shape[:-1]
+    x2 = _as2d(_bf16_rows(x, "gemm_silu_mul input"))
+    if x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
+        x2 = x2.contiguous()
+    M, K = x2.shape
+    I = w_pairs.shape[0] // 2
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=x.device)
+    if M:
+        _abi.check(_lib.b2_gemm_silu_mul(get_runtime().ctx, x2.data_ptr(), x2.stride(0), w_pairs.data_ptr(), w_pairs.stride(0),
+                                         out.data_ptr(), out.stride(0), M, I, K, _stream()), "b2_gemm_silu_mul")
+    return out.view(*lead, I)
+
+
 def _two_shot_min_tokens(world: int) -> int:
     """From this many tokens on the two-shot kernel is used.  One-shot pushes (world-1) copies of the partial,
     two-shot 2 (world-1)/world: the same at world 2, 4.6x less at world 8."""

@@ -79,6 +79,39 @@ def test_gemm_repeatable_and_counters_clean(ops, rt):
     assert_close_bf16(b, a.float(), "second launch", abs_tol=2e-3, rel_tol=4e-3)
 
 
+@pytest.mark.parametrize("m,i,k", [(64, 12288, 4096), (64, 1536, 4096), (7, 256, 512), (300, 1024, 1024), (1100, 3072, 1024)])
+def test_gemm_silu_mul(ops, rt, m, i, k):
+    """gate_up GEMM with SiLU * mul in the epilogue against gemm followed by the oracle's activation."""
+    g = torch.Generator().manual_seed(m + i)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    wg = (torch.randn(i, k, generator=g) * 0.05).bfloat16()
+    wu = (torch.randn(i, k, generator=g) * 0.05).bfloat16()
+    pairs = torch.stack((wg, wu), dim=1).reshape(2 * i, k).contiguous()
+    got = ops.gemm_silu_mul(x.to(DEV), pairs.to(DEV))
+    torch.cuda.synchronize()
+    rt.check_status()
+    ref = O.silu_and_mul(torch.cat([O.linear(x, wg), O.linear(x, wu)], dim=-1))
+    exact = torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
+    assert_close_bf16(got, exact, f"gemm_silu_mul {m}x{i}x{k}", abs_tol=3e-2, rel_tol=2e-2)
+    assert ulp_mismatch_fraction(got, ref, 2) < 2e-2  # same roundings as the two-kernel form, up to the GEMM's own last-bit differences
+
+
+def test_merged_column_layer_paired_weight(pkg, rt, golden_dir):
+    from nanovllm_b200.layers.linear import MergedColumnParallelLinear
+    d = torch.load(os.path.join(golden_dir, "col.pt"))
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        layer = MergedColumnParallelLinear(128, [192 * 1, 192 * 1]).to(DEV)  # world 1: both halves whole
+    finally:
+        torch.set_default_dtype(torch.float32)
+    layer.weight.weight_loader(layer.weight, d["wg"].to(DEV), 0)
+    layer.weight.weight_loader(layer.weight, d["wu"].to(DEV), 1)
+    x = d["x"].to(DEV)
+    y = layer(x)
+    act = layer.forward_silu_mul(x)
+    assert ulp_mismatch_fraction(act, O.silu_and_mul(y.cpu()), 2) < 2e-2
+
+
 def test_column_parallel_golden(ops, golden_dir):
     d = torch.load(os.path.join(golden_dir, "col.pt"))
     for r in range(2):
