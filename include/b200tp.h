@@ -109,6 +109,21 @@ int64_t b2_launch_count(void);
 int b2_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias,
             void* C, int64_t ldc, int M, int N, int K, void* stream);
 
+/* ---- qkv projection with the per-head work that follows it: replaces
+ *      QKVParallelLinear.forward (nanovllm/layers/linear.py:73), q_norm / k_norm
+ *      (nanovllm/models/qwen3.py:82-84), the rotary embedding (:85) and
+ *      store_kvcache (nanovllm/layers/attention.py:59-63) -----------------------
+ * qkv[M, (nq + 2 nkv) head_dim] = A W^T (+ bias); then, per token and head:
+ * q and k heads are RMS-normalised (weights may both be NULL) and rotated,
+ * k and v heads are also written to the paged cache (k_cache may be NULL).
+ * Arguments as b2_gemm and b2_qk_norm_rope_store.  For up to 64 tokens and
+ * head_dim 128 everything happens in the GEMM's epilogue (one launch);
+ * otherwise the projection and the head kernel run as two launches. */
+int b2_qkv_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias, void* qkv,
+                 int64_t ld_qkv, int M, int nq, int nkv, int head_dim, int K, const void* q_norm_w,
+                 const void* k_norm_w, float eps, const int64_t* positions, const float* cos_sin, void* k_cache,
+                 void* v_cache, const int32_t* slot_mapping, void* stream);
+
 /* ---- gate_up projection fused with SiLU(gate) * up: replaces the pair
  *      MergedColumnParallelLinear.forward + SiluAndMul.forward in Qwen3MLP
  *      (nanovllm/models/qwen3.py:113-116; nanovllm/layers/activation.py:8-11) --

@@ -48,6 +48,7 @@ SIGNATURES = {
     "b2_status_clear": [_p],
     "b2_trace": [_p, _i, _p, _i],
     "b2_gemm": [_p, _p, _i64, _p, _i64, _p, _p, _i64, _i, _i, _i, _p],
+    "b2_qkv_fused": [_p, _p, _i64, _p, _i64, _p, _p, _i64, _i, _i, _i, _i, _i, _p, _p, _f, _p, _p, _p, _p, _p, _p],
     "b2_gemm_silu_mul": [_p, _p, _i64, _p, _i64, _p, _i64, _i, _i, _i, _p],
     "b2_gemm_static_scratch": [_p, _i64, _p, _i64, _p, _p, _i64, _i, _i, _i, _p],
     "b2_rowpar_fused": [_p, _p, _i64, _p, _i64, _p, _i, _i, _i, _p, _p, _f, _p, _p, _p],

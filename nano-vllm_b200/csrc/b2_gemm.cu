@@ -58,6 +58,16 @@ struct GemmArgs {
   uint16_t* C;
   int64_t ldc;
   const uint16_t* bias;
+  // qkv projection fused with q/k head norm + RoPE + KV scatter (cluster kernel only; one 128-wide head per tile)
+  int qkv_fused, nq, nkv;
+  const int64_t* positions;
+  const float* cos_sin;
+  const uint16_t* q_norm_w;
+  const uint16_t* k_norm_w;
+  float qk_eps;
+  uint16_t* k_cache;
+  uint16_t* v_cache;
+  const int32_t* slots;
   int silu_pairs;  // 1: features come in (gate, up) pairs; store silu(gate) * up, one value per pair, at column feature / 2
   // stream-K combine
   float* ws;
@@ -859,6 +869,12 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
   if (threadIdx.x == 0) b2::pdl_launch_dependents();
   if (threadIdx.x == 0) stamp(a, 0);
   unsigned int parity = 0;
+  // fused qkv heads: rotary factors and cache slots of the first rows this warp will finish, fetched while the
+  // mainloop runs (the epilogue warps have nothing else to do then), so that the launch does not end on a chain of
+  // dependent global loads
+  constexpr int PRE_ROWS = 8;
+  float pre_cs[PRE_ROWS][4];
+  int pre_slot[PRE_ROWS];
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -913,6 +929,24 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
     const int f = q * 32 + lane;  // feature row of the tile this thread holds
     b2::pdl_wait();
     if (EPI != EPI_STORE) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
+    if (EPI == EPI_STORE && a.qkv_fused) {
+      const bool rotated = tile < a.nq + a.nkv;
+#pragma unroll
+      for (int i = 0; i < PRE_ROWS; ++i) {
+        const int lt = (warp - 2) + 4 * i;
+        const int token = (((lt >> 2) * S + crank) << 2) + (lt & 3);
+        pre_slot[i] = -1;
+        pre_cs[i][0] = pre_cs[i][1] = pre_cs[i][2] = pre_cs[i][3] = 0.f;
+        if (token < a.M && (lt >> 2) * S + crank < C::GROUPS) {
+          if (a.k_cache != nullptr && tile >= a.nq) pre_slot[i] = __ldg(a.slots + token);
+          if (rotated) {
+            const float* cs = a.cos_sin + __ldg(a.positions + token) * 128;
+            pre_cs[i][0] = __ldg(cs + lane * 2); pre_cs[i][1] = __ldg(cs + lane * 2 + 1);
+            pre_cs[i][2] = __ldg(cs + 64 + lane * 2); pre_cs[i][3] = __ldg(cs + 64 + lane * 2 + 1);
+          }
+        }
+      }
+    }
     if (b2::mbar_wait(bar_tfull, 0, abort_flag, PIPE_LIMIT_NS, B2_WAIT_TMEM_FULL)) {
       b2::tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
@@ -963,6 +997,72 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
       owned = gl + 1;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+    if (EPI == EPI_STORE && a.qkv_fused) {
+      // The tile is one attention head (128 features) and out_buf holds whole head rows of the tokens this CTA
+      // owns: finish the head here.  One warp per token row; lane l holds dims (2l, 2l+1) of both halves.
+      // q and k heads: RMSNorm over the head (nanovllm/models/qwen3.py:82-84), neox RoPE
+      // (nanovllm/layers/rotary_embedding.py:6-14); k and v heads also go to the paged cache
+      // (nanovllm/layers/attention.py:21-30).  Same arithmetic and roundings as qk_norm_rope_store_kernel.
+      const bool is_q = tile < a.nq, is_k = !is_q && tile < a.nq + a.nkv;
+      const int kvh = is_k ? tile - a.nq : tile - a.nq - a.nkv;
+      const uint16_t* nw = (is_q || is_k) ? (is_q ? a.q_norm_w : a.k_norm_w) : nullptr;
+      float nw1[2] = {1.f, 1.f}, nw2[2] = {1.f, 1.f};
+      if (nw != nullptr) {
+        nw1[0] = __uint_as_float(static_cast<uint32_t>(nw[lane * 2]) << 16); nw1[1] = __uint_as_float(static_cast<uint32_t>(nw[lane * 2 + 1]) << 16);
+        nw2[0] = __uint_as_float(static_cast<uint32_t>(nw[64 + lane * 2]) << 16); nw2[1] = __uint_as_float(static_cast<uint32_t>(nw[64 + lane * 2 + 1]) << 16);
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {  // at most 64 owned rows, 4 warps
+        const int lt = (warp - 2) + 4 * i;
+        if (lt >= owned * 4) break;
+        const int token = (((lt >> 2) * S + crank) << 2) + (lt & 3);
+        if (token >= a.M) continue;
+        const uint16_t* row = out16 + lt * BM;
+        uint32_t lo = *reinterpret_cast<const uint32_t*>(row + lane * 2);
+        uint32_t hi = *reinterpret_cast<const uint32_t*>(row + 64 + lane * 2);
+        int slot;
+        float cs4[4];
+        if (i < PRE_ROWS) {
+          slot = pre_slot[i];
+          cs4[0] = pre_cs[i][0]; cs4[1] = pre_cs[i][1]; cs4[2] = pre_cs[i][2]; cs4[3] = pre_cs[i][3];
+        } else {  // more rows than were prefetched (no K split: the CTA owns all 64 tokens)
+          slot = (a.k_cache != nullptr && !is_q) ? __ldg(a.slots + token) : -1;
+          const float* cs = a.cos_sin + __ldg(a.positions + token) * 128;
+          cs4[0] = __ldg(cs + lane * 2); cs4[1] = __ldg(cs + lane * 2 + 1);
+          cs4[2] = __ldg(cs + 64 + lane * 2); cs4[3] = __ldg(cs + 64 + lane * 2 + 1);
+        }
+        if (is_q || is_k) {
+          float x1[2] = {b2::bf16_lo(lo), b2::bf16_hi(lo)}, x2[2] = {b2::bf16_lo(hi), b2::bf16_hi(hi)};
+          if (nw != nullptr) {
+            float ss = x1[0] * x1[0] + x2[0] * x2[0] + x1[1] * x1[1] + x2[1] * x2[1];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float rstd = rsqrtf(ss / 128.0f + a.qk_eps);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              x1[e] = b2::bf16_round(b2::bf16_round(x1[e] * rstd) * nw1[e]);
+              x2[e] = b2::bf16_round(b2::bf16_round(x2[e] * rstd) * nw2[e]);
+            }
+          }
+          float y1[2], y2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            y1[e] = __fsub_rn(__fmul_rn(x1[e], cs4[e]), __fmul_rn(x2[e], cs4[2 + e]));
+            y2[e] = __fadd_rn(__fmul_rn(x2[e], cs4[e]), __fmul_rn(x1[e], cs4[2 + e]));
+          }
+          lo = b2::pack_bf16(y1[0], y1[1]);
+          hi = b2::pack_bf16(y2[0], y2[1]);
+        }
+        uint16_t* dst = a.C + token * a.ldc + tile * BM;
+        *reinterpret_cast<uint32_t*>(dst + lane * 2) = lo;
+        *reinterpret_cast<uint32_t*>(dst + 64 + lane * 2) = hi;
+        if (slot >= 0) {
+          uint16_t* cache = (is_k ? a.k_cache : a.v_cache) + (static_cast<int64_t>(slot) * a.nkv + kvh) * 128;
+          *reinterpret_cast<uint32_t*>(cache + lane * 2) = lo;
+          *reinterpret_cast<uint32_t*>(cache + 64 + lane * 2) = hi;
+        }
+      }
+    } else {
     // rows of out_buf: local token index lt = gl * 4 + j  <->  token (gl * S + crank) * 4 + j; 16 pieces of 16 bytes per row
     const int et = threadIdx.x - 64;
     for (int idx = et; idx < owned * 4 * 16; idx += 128) {
@@ -983,6 +1083,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
             if (r < a.world) *reinterpret_cast<uint4*>(a.inbox[r] + off) = w;
         }
       }
+    }
     }
     if (warp == 2 && lane == 0) stamp(a, 4);
   }
@@ -1064,6 +1165,8 @@ int max_resident_clusters(int S) {
   return n;
 }
 
+thread_local int g_last_gemm_path = 0;  // 0 = stream-K kernel, 1 = cluster kernel (set by launch_gemm)
+
 bool cluster_path_enabled() {
   static const bool on = [] {
     const char* e = getenv("B2_CLUSTER");
@@ -1136,11 +1239,13 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
   rc = b2::encode_tmap_2d(&tmQ, pQ, K, rowsQ, ldQ, BK, bn);
   if (rc != B2_OK) return rc;
 
+  g_last_gemm_path = 0;
   if constexpr (EPI != EPI_PUSH2) {
     if (swap && args.tilesQ == 1 && bn <= 64) {  // up to 64 tokens: the decode sizes
       const int S = bn == 32 ? pick_cluster_split<32, EPI>(args.tilesP, args.kblocks, ctx->num_sms)
                              : pick_cluster_split<64, EPI>(args.tilesP, args.kblocks, ctx->num_sms);
       if (S > 0) {
+        g_last_gemm_path = 1;
         args.gemm_ctas = args.tilesP * S;
         if (bn == 32) return launch_cluster_inst<32, EPI>(tmP, tmQ, args, args.tilesP, S, stream);
         return launch_cluster_inst<64, EPI>(tmP, tmQ, args, args.tilesP, S, stream);
@@ -1267,6 +1372,43 @@ int b2_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw,
   args.ldc = ldc;
   args.bias = static_cast<const uint16_t*>(bias);
   return launch_gemm<EPI_STORE>(ctx, A, lda, W, ldw, M, N, K, args, 0, static_cast<cudaStream_t>(stream));
+}
+
+int b2_qkv_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias, void* qkv, int64_t ld_qkv, int M,
+                 int nq, int nkv, int head_dim, int K, const void* q_norm_w, const void* k_norm_w, float eps, const int64_t* positions,
+                 const float* cos_sin, void* k_cache, void* v_cache, const int32_t* slot_mapping, void* stream) {
+  if (ctx == nullptr || nq <= 0 || nkv <= 0 || (head_dim != 128 && head_dim != 64)) return B2_ERR_ARG;
+  const int N = (nq + 2 * nkv) * head_dim;
+  int rc = check_operands(A, lda, W, ldw, M, N, K);
+  if (rc != B2_OK) return rc;
+  if (M == 0) return B2_OK;
+  if (!qkv || !aligned16(qkv) || ld_qkv % 8 != 0 || ld_qkv < N || !positions || !cos_sin) return B2_ERR_ARG;
+  if ((q_norm_w == nullptr) != (k_norm_w == nullptr)) return B2_ERR_ARG;
+  if (k_cache != nullptr && (!v_cache || !slot_mapping)) return B2_ERR_ARG;
+  if (bias != nullptr && !aligned16(bias)) return B2_ERR_ARG;
+  GemmArgs args{};
+  args.C = static_cast<uint16_t*>(qkv);
+  args.ldc = ld_qkv;
+  args.bias = static_cast<const uint16_t*>(bias);
+  if (head_dim == 128) {  // one head per 128-feature tile: the cluster kernel can finish the heads itself
+    args.qkv_fused = 1;
+    args.nq = nq;
+    args.nkv = nkv;
+    args.positions = positions;
+    args.cos_sin = cos_sin;
+    args.q_norm_w = static_cast<const uint16_t*>(q_norm_w);
+    args.k_norm_w = static_cast<const uint16_t*>(k_norm_w);
+    args.qk_eps = eps;
+    args.k_cache = static_cast<uint16_t*>(k_cache);
+    args.v_cache = static_cast<uint16_t*>(v_cache);
+    args.slots = slot_mapping;
+  }
+  rc = launch_gemm<EPI_STORE>(ctx, A, lda, W, ldw, M, N, K, args, 0, static_cast<cudaStream_t>(stream));
+  if (rc != B2_OK) return rc;
+  if (args.qkv_fused && g_last_gemm_path == 1) return B2_OK;
+  // many tokens (or 64-wide heads): the projection ran on the stream-K kernel; finish the heads in a second launch
+  return b2_qk_norm_rope_store(qkv, ld_qkv, M, nq, nkv, head_dim, q_norm_w, k_norm_w, eps, positions, cos_sin, k_cache, v_cache, slot_mapping,
+                               stream);
 }
 
 int b2_gemm_silu_mul(b2_ctx* ctx, const void* A, int64_t lda, const void* W_pairs, int64_t ldw, void* out, int64_t ldo, int M, int I, int K,

@@ -7,7 +7,7 @@ same tensors.  The data flow differs in where the norms run:
   reference (:146-159)                      here
   --------------------------------------   ------------------------------------------
   h, res = input_layernorm(h, res)          (done by the previous layer's down_proj launch)
-  h = attn(h)          # o_proj + NCCL      qkv GEMM; q/k-norm + RoPE + KV scatter (1 kernel);
+  h = attn(h)          # o_proj + NCCL      qkv GEMM with q/k-norm + RoPE + KV scatter in its epilogue;
   h, res = post_attention_layernorm(h,res)  attention (library); o_proj GEMM + cross-GPU sum
   h = mlp(h)           # down_proj + NCCL     + residual + post_attention_layernorm (1 kernel);
                                             gate_up GEMM with SiLU*mul in its epilogue; down_proj GEMM + cross-GPU
@@ -55,14 +55,14 @@ class Qwen3Attention(nn.Module):
 
     def attention_output(self, positions: torch.Tensor, hidden_states: torch.Tensor) -> torch.Tensor:
         """Everything up to (not including) o_proj: returns [T, q_size]."""
-        qkv = self.qkv_proj(hidden_states)
         ctx = get_context()
         have_cache = self.attn.k_cache.numel() > 0
-        ops.qk_norm_rope_store(qkv, self.num_heads, self.num_kv_heads, self.head_dim,
-                               None if self.qkv_bias else self.q_norm.weight, None if self.qkv_bias else self.k_norm.weight,
-                               self.rms_norm_eps, positions, self.rotary_emb.cos_sin_cache,
-                               self.attn.k_cache if have_cache else None, self.attn.v_cache if have_cache else None,
-                               ctx.slot_mapping if have_cache else None)
+        # projection, q/k head norm, RoPE and the K/V scatter: one launch for decode-sized batches, two otherwise
+        qkv = ops.qkv_fused(hidden_states, self.qkv_proj.weight, self.qkv_proj.bias, self.num_heads, self.num_kv_heads, self.head_dim,
+                            None if self.qkv_bias else self.q_norm.weight, None if self.qkv_bias else self.k_norm.weight,
+                            self.rms_norm_eps, positions, self.rotary_emb.cos_sin_cache,
+                            self.attn.k_cache if have_cache else None, self.attn.v_cache if have_cache else None,
+                            ctx.slot_mapping if have_cache else None)
         q, k, v = qkv.split([self.q_size, self.kv_size, self.kv_size], dim=-1)
         o = self.attn.attend(q.view(-1, self.num_heads, self.head_dim), k.view(-1, self.num_kv_heads, self.head_dim),
                              v.view(-1, self.num_kv_heads, self.head_dim))

@@ -46,6 +46,31 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> 
     return out.view(*lead, N)
 
 
+def qkv_fused(x: torch.Tensor, w: torch.Tensor, bias, nq: int, nkv: int, head_dim: int, q_norm_w, k_norm_w, eps: float,
+              positions: torch.Tensor, cos_sin: torch.Tensor, k_cache, v_cache, slot_mapping) -> torch.Tensor:
+    """qkv projection + q/k head norm + RoPE + KV scatter; returns the [M, (nq + 2 nkv) head_dim] tensor with q and k
+    already normalised and rotated."""
+    x2 = _as2d(_bf16_rows(x, "qkv input"))
+    if x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
+        x2 = x2.contiguous()
+    M, K = x2.shape
+    N = w.shape[0]
+    assert N == (nq + 2 * nkv) * head_dim
+    assert positions.dtype == torch.int64 and cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
+    have_cache = k_cache is not None and k_cache.numel() > 0
+    if have_cache:
+        assert k_cache.stride(1) == nkv * head_dim and slot_mapping.dtype == torch.int32
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    if M:
+        _abi.check(_lib.b2_qkv_fused(get_runtime().ctx, x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0),
+                                     bias.data_ptr() if bias is not None else None, out.data_ptr(), out.stride(0), M, nq, nkv, head_dim, K,
+                                     q_norm_w.data_ptr() if q_norm_w is not None else None, k_norm_w.data_ptr() if k_norm_w is not None else None,
+                                     float(eps), positions.data_ptr(), cos_sin.data_ptr(), k_cache.data_ptr() if have_cache else None,
+                                     v_cache.data_ptr() if have_cache else None, slot_mapping.data_ptr() if have_cache else None, _stream()),
+                   "b2_qkv_fused")
+    return out
+
+
 def gemm_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor) -> torch.Tensor:
     """silu(x @ gate^T) * (x @ up^T) where w_pairs interleaves gate and up rows (gate_0, up_0, gate_1, ...)."""
     lead = x.shape[:-1]

@@ -96,6 +96,36 @@ def test_gemm_silu_mul(ops, rt, m, i, k):
     assert ulp_mismatch_fraction(got, ref, 2) < 2e-2  # same roundings as the two-kernel form, up to the GEMM's own last-bit differences
 
 
+@pytest.mark.parametrize("m,nq,nkv,k", [(64, 32, 8, 4096), (64, 4, 1, 4096), (9, 4, 2, 512), (300, 4, 2, 512)])
+def test_qkv_fused_matches_two_kernel_form(ops, rt, m, nq, nkv, k):
+    """Projection + head norm + RoPE + KV scatter in one call against gemm followed by the head kernel."""
+    hd = 128
+    g = torch.Generator().manual_seed(m + nq)
+    x = torch.randn(m, k, generator=g).bfloat16().to(DEV)
+    w = (torch.randn((nq + 2 * nkv) * hd, k, generator=g) * 0.05).bfloat16().to(DEV)
+    qw = (torch.rand(hd, generator=g) + 0.5).bfloat16().to(DEV)
+    kw = (torch.rand(hd, generator=g) + 0.5).bfloat16().to(DEV)
+    pos = torch.randint(0, 512, (m,), generator=g).to(DEV)
+    cache = O.rope_cache(hd, 512, 1e6).to(DEV)
+    slots = torch.randperm(4 * 256, generator=g)[:m].to(torch.int32)
+    slots[::7] = -1
+    slots = slots.to(DEV)
+    kc1 = torch.zeros(4, 256, nkv, hd, dtype=torch.bfloat16, device=DEV)
+    vc1, kc2, vc2 = torch.zeros_like(kc1), torch.zeros_like(kc1), torch.zeros_like(kc1)
+    fused = ops.qkv_fused(x, w, None, nq, nkv, hd, qw, kw, 1e-6, pos, cache, kc1, vc1, slots)
+    two = ops.gemm(x, w)
+    ops.qk_norm_rope_store(two, nq, nkv, hd, qw, kw, 1e-6, pos, cache, kc2, vc2, slots)
+    torch.cuda.synchronize()
+    rt.check_status()
+    assert torch.equal(fused, two)
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    # and against the oracle's statement of the same steps
+    y = O.linear(x.cpu(), w.cpu())
+    q, kk, v = y.split([nq * hd, nkv * hd, nkv * hd], dim=-1)
+    q_ref = O.apply_rope(O.rms_norm(q.reshape(m, nq, hd), qw.cpu(), 1e-6), pos.cpu(), cache.cpu())
+    assert ulp_mismatch_fraction(fused[:, :nq * hd].cpu().reshape(m, nq, hd), q_ref, 2) < 2e-2
+
+
 def test_merged_column_layer_paired_weight(pkg, rt, golden_dir):
     from nanovllm_b200.layers.linear import MergedColumnParallelLinear
     d = torch.load(os.path.join(golden_dir, "col.pt"))
