@@ -258,6 +258,16 @@ def run_b200(args) -> None:
         except Exception as ex:  # the comparison is informative only
             block_cmp = {"error": repr(ex)[:200]}
 
+    # ---- the whole model forward next to the reference's formulation of it (cuBLAS + NCCL + compiled elementwise) ----
+    forward_cmp = None
+    if not args.skip_nccl:
+        try:
+            from nanovllm_b200 import rowpar_microbench as mb
+            resident.load(fresh_seqs())
+            forward_cmp = mb.compare_model_forward(runner, BATCH)
+        except Exception as ex:
+            forward_cmp = {"error": repr(ex)[:300]}
+
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         ref = cpu_reference(1, 1, 64, max_seconds=15.0)
@@ -271,6 +281,8 @@ def run_b200(args) -> None:
                 "gpu_launches": launches, "roofline": roofline, "step_roofline": step_roof, "cpu_baseline": cpu}
         if block_cmp is not None:
             line["rowpar_block_us"] = block_cmp
+        if forward_cmp is not None:
+            line["model_forward_us"] = forward_cmp
         print(json.dumps(line), flush=True)
     runner.exit()
     dist.destroy_process_group()

@@ -116,6 +116,112 @@ def compare_blocks(blocks, peaks: dict, iters: int = 200, with_nccl: bool = True
     return out
 
 
+def compare_model_forward(runner, bs: int, iters: int = 20) -> dict:
+    """One decode forward pass of the runner's model (all decoder layers, batch `bs`) in two forms, each in
+    its own CUDA graph on the same weights, KV cache and batch state:
+      ours      - the runner's captured graph (fused kernels of this library)
+      reference - the reference's formulation of the same pass: F.linear for every projection
+                  (nanovllm/layers/linear.py:73,153), NCCL all_reduce after o_proj and down_proj (:155),
+                  torch.compile'd RMSNorm / add+RMSNorm / RoPE / SiLU*mul (nanovllm/layers/layernorm.py,
+                  rotary_embedding.py, activation.py), an index_copy_ for the KV scatter, and the same
+                  flash-attn decode call (nanovllm/layers/attention.py:72-74).
+    Returns microseconds per pass (max over ranks)."""
+    from flash_attn import flash_attn_with_kvcache
+    from .utils.context import set_context, reset_context
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    model = runner.model.model
+    gv = runner.graph_vars
+    eps = runner.config.rms_norm_eps
+
+    def _rms(x, w):
+        dt = x.dtype
+        x = x.float()
+        var = x.pow(2).mean(dim=-1, keepdim=True)
+        x.mul_(torch.rsqrt(var + eps))
+        return x.to(dt).mul_(w)
+
+    def _rope(cos_sin, q, k):
+        cos, sin = cos_sin.chunk(2, dim=-1)
+
+        def rot(x):
+            x1, x2 = torch.chunk(x.float(), 2, dim=-1)
+            return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).to(x.dtype)
+        return rot(q), rot(k)
+
+    def _silu_mul(x):
+        a, b = x.chunk(2, -1)
+        return F.silu(a) * b
+
+    try:
+        rms, add_rms, rope, silu_mul = (torch.compile(f) for f in (_rms, lambda x, r, w: _reference_add_rms(x, r, w, eps), _rope, _silu_mul))
+    except Exception:
+        rms, add_rms, rope, silu_mul = _rms, (lambda x, r, w: _reference_add_rms(x, r, w, eps)), _rope, _silu_mul
+
+    @torch.inference_mode()
+    def reference_pass():
+        ids, pos = gv["input_ids"][:bs], gv["positions"][:bs]
+        slots, lens, tables = gv["slot_mapping"][:bs].long(), gv["context_lens"][:bs], gv["block_tables"][:bs]
+        emb = model.embed_tokens
+        if world > 1:
+            mask = (ids >= emb.vocab_start_idx) & (ids < emb.vocab_end_idx)
+            h = F.embedding(mask * (ids - emb.vocab_start_idx), emb.weight) * mask.unsqueeze(1)
+            dist.all_reduce(h)
+        else:
+            h = F.embedding(ids, emb.weight)
+        residual = None
+        y = h
+        for layer in model.layers:
+            att = layer.self_attn
+            if residual is None:
+                residual, h = y, rms(y, layer.input_layernorm.weight)
+            else:
+                h, residual = add_rms(y, residual, layer.input_layernorm.weight)
+            qkv = F.linear(h, att.qkv_proj.weight)
+            q, k, v = qkv.split([att.q_size, att.kv_size, att.kv_size], dim=-1)
+            q = rms(q.view(-1, att.num_heads, att.head_dim), att.q_norm.weight)
+            k = rms(k.view(-1, att.num_kv_heads, att.head_dim), att.k_norm.weight)
+            q, k = rope(att.rotary_emb.cos_sin_cache[pos].unsqueeze(1), q, k)
+            kc, vc = att.attn.k_cache, att.attn.v_cache
+            kc.view(-1, att.num_kv_heads, att.head_dim).index_copy_(0, slots, k)
+            vc.view(-1, att.num_kv_heads, att.head_dim).index_copy_(0, slots, v.view(-1, att.num_kv_heads, att.head_dim))
+            o = flash_attn_with_kvcache(q.unsqueeze(1), kc, vc, cache_seqlens=lens, block_table=tables, softmax_scale=att.scaling, causal=True)
+            y = F.linear(o.flatten(1, -1), att.o_proj.weight)
+            if world > 1:
+                dist.all_reduce(y)
+            h, residual = add_rms(y, residual, layer.post_attention_layernorm.weight)
+            act = silu_mul(F.linear(h, layer.mlp.gate_up_proj.weight))
+            y = F.linear(act, layer.mlp.down_proj.weight)
+            if world > 1:
+                dist.all_reduce(y)
+        out, _ = add_rms(y, residual, model.norm.weight)
+        return out
+
+    for _ in range(3):
+        reference_pass()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        reference_pass()
+
+    def timed(replay):
+        replay()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return _max_over_ranks(e0.elapsed_time(e1) * 1e3 / iters)
+
+    ref_us = timed(graph.replay)
+    ours_us = timed(runner.graphs[bs].replay)
+    return {"b200_us": ours_us, "reference_formulation_nccl_us": ref_us, "speedup": ref_us / ours_us, "batch": bs, "tp": world,
+            "what": "model forward only (embedding, all decoder layers, final norm); LM head and sampling excluded on both sides"}
+
+
 def main():
     import argparse
     here = os.path.dirname(os.path.abspath(__file__))

@@ -170,6 +170,46 @@ def _worker(rank: int, world: int, port: int):
         dist.destroy_process_group()
 
 
+def _timeout_worker(rank: int, world: int, port: int):
+    """Failure made on the host: rank 1 never issues its half of a fused call.  Rank 0's kernel waits for the
+    partial rows, gives up after the context's limit, reports it through the status word and ends normally."""
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import __graft_entry__ as entry
+    entry.load_package()
+    from nanovllm_b200 import ops, _abi
+    from nanovllm_b200.runtime import init_runtime, shutdown_runtime
+    from oracle import tp_path as O
+    dev = torch.device("cuda", rank)
+    rt = init_runtime(max_tokens=256, hidden=1024, oneshot_tokens=256, timeout_ms=300)
+    try:
+        xs, ws, residual, norm_w = O.rowpar_case(16, 1024, 1024, world, seed=1)
+        # a healthy call first
+        ops.rowpar_fused(xs[rank].to(dev), ws[rank].to(dev), None, residual.to(dev), norm_w.to(dev), 1e-6)
+        torch.cuda.synchronize()
+        rt.check_status()
+        dist.barrier()
+        if rank == 0:
+            ops.rowpar_fused(xs[0].to(dev), ws[0].to(dev), None, residual.to(dev), norm_w.to(dev), 1e-6)
+            torch.cuda.synchronize()  # returns: the wait is bounded
+            with pytest.raises(_abi.B2Error, match="partial rows never arrived"):
+                rt.check_status()
+            # the device is still usable after the expired wait
+            assert torch.ones(4, device=dev).sum().item() == 4.0
+        dist.barrier()  # rank 1 has launched nothing in between
+    finally:
+        shutdown_runtime()
+        dist.destroy_process_group()
+
+
+def test_expired_wait_is_reported_not_hung():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mp.spawn(_timeout_worker, args=(2, 29790), nprocs=2, join=True)
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_tensor_parallel_ranks(world):
     if torch.cuda.device_count() < world:
