@@ -6,6 +6,9 @@ few GB, so a `--set full` capture of 1-3 launches ends by itself).
 
 cases:
   gemm_decode     column-parallel GEMM, M=64, N=24576, K=4096 (Qwen3-8B gate_up at TP=1), 4 weight copies
+  silu_decode     the same GEMM with SiLU*mul in its epilogue (what the decoder layer launches)
+  qkv_decode      qkv projection M=64, N=6144, K=4096 with q/k-norm + RoPE + KV scatter in its epilogue, 8 weight copies
+  oproj_decode    fused row-parallel launch, M=64, N=4096, Kr=4096 (Qwen3-8B o_proj at TP=1), 8 weight copies
   gemm_prefill    GEMM M=4096, N=4096, K=4096
   rowpar_decode   fused row-parallel launch, M=64, N=4096, Kr=12288 (Qwen3-8B down_proj at TP=1)
   rowpar_prefill  fused row-parallel launch, M=1024, N=5120, Kr=1024
@@ -49,8 +52,25 @@ def main():
         m, n, k, copies = (64, 24576, 4096, 4) if a.case == "gemm_decode" else (4096, 4096, 4096, 2)
         x, ws = rnd(m, k), [rnd(n, k, scale=0.02) for _ in range(copies)]
         call = lambda i: ops.gemm(x, ws[i % copies])
-    elif a.case in ("rowpar_decode", "rowpar_prefill"):
-        m, n, k, copies = (64, 4096, 12288, 4) if a.case == "rowpar_decode" else (1024, 5120, 1024, 8)
+    elif a.case == "silu_decode":
+        m, i, k, copies = 64, 12288, 4096, 4
+        x, ws = rnd(m, k), [rnd(2 * i, k, scale=0.02) for _ in range(copies)]
+        call = lambda j: ops.gemm_silu_mul(x, ws[j % copies])
+    elif a.case == "qkv_decode":
+        m, nq, nkv, k, copies = 64, 32, 8, 4096, 8
+        x, ws = rnd(m, k), [rnd((nq + 2 * nkv) * 128, k, scale=0.02) for _ in range(copies)]
+        qw, kw = rnd(128), rnd(128)
+        pos = torch.randint(0, 2048, (m,), device=dev)
+        t = torch.arange(2048, dtype=torch.float, device=dev)
+        inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2, dtype=torch.float, device=dev) / 128))
+        fr = torch.outer(t, inv)
+        cos_sin = torch.cat((fr.cos(), fr.sin()), dim=-1).contiguous()
+        kc = torch.zeros(16, 256, nkv, 128, dtype=torch.bfloat16, device=dev)
+        vc = torch.zeros_like(kc)
+        slots = torch.randperm(16 * 256, device=dev)[:m].to(torch.int32)
+        call = lambda j: ops.qkv_fused(x, ws[j % copies], None, nq, nkv, 128, qw, kw, 1e-6, pos, cos_sin, kc, vc, slots)
+    elif a.case in ("rowpar_decode", "rowpar_prefill", "oproj_decode"):
+        m, n, k, copies = {"rowpar_decode": (64, 4096, 12288, 4), "rowpar_prefill": (1024, 5120, 1024, 8), "oproj_decode": (64, 4096, 4096, 8)}[a.case]
         x, ws, res, nw = rnd(m, k), [rnd(n, k, scale=0.02) for _ in range(copies)], rnd(m, n), rnd(n)
         call = lambda i: ops.rowpar_fused(x, ws[i % copies], None, res, nw, 1e-6)
     elif a.case == "store_kvcache":
