@@ -2,6 +2,8 @@
 // residual add), SiLU*mul, fused q/k-norm + RoPE + KV scatter, embedding
 // lookup with owner-rank broadcast, greedy argmax.  All accesses are 16-byte
 // vectors on the contiguous dimension.
+#include <algorithm>
+
 #include "b2_common.cuh"
 
 namespace {
@@ -324,40 +326,58 @@ __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
 }
 
 // ---------------------------------------------------------------------------
-// argmax over each row (first index wins ties)
+// argmax over each row (first index wins ties).  A row is split over several blocks; each block folds its
+// columns into one 64-bit key (value bits made order-preserving in the high word, ~index in the low word) and
+// atomicMax-es it into the row's output word; a second tiny kernel turns the winning key back into the index.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) argmax_kernel(const uint16_t* __restrict__ logits, int64_t ld, int V, int64_t* __restrict__ out) {
+__device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
+  uint32_t b = __float_as_uint(v);
+  b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);  // monotone map float -> uint
+  return (static_cast<unsigned long long>(b) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(idx));
+}
+
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const uint16_t* __restrict__ logits, int64_t ld, int V, int cols_per_block,
+                                                             unsigned long long* __restrict__ keys) {
   b2::pdl_launch_dependents();
   b2::pdl_wait();
   const uint16_t* row = logits + blockIdx.x * ld;
+  const int c0 = blockIdx.y * cols_per_block, c1 = min(V, c0 + cols_per_block);
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  const int nvec = V >> 3;
-  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+  const int v0 = c0 >> 3, v1 = c1 >> 3;  // cols_per_block is a multiple of 8
+  for (int v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
     float f[8];
     unpack8(ldg_v4(row + v * 8), f);
 #pragma unroll
     for (int e = 0; e < 8; ++e)
       if (f[e] > best) { best = f[e]; best_i = v * 8 + e; }
   }
-  for (int i = nvec * 8 + threadIdx.x; i < V; i += blockDim.x) {
+  for (int i = max(c0, v1 * 8) + threadIdx.x; i < c1; i += blockDim.x) {
     const float f = __uint_as_float(static_cast<uint32_t>(row[i]) << 16);
     if (f > best || (f == best && i < best_i)) { best = f; best_i = i; }
   }
+  unsigned long long key = best_i == 0x7fffffff ? 0ull : argmax_key(best, best_i);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-    if (ob > best || (ob == best && oi < best_i)) { best = ob; best_i = oi; }
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+    key = other > key ? other : key;
   }
-  __shared__ float sb[8];
-  __shared__ int si[8];
-  if ((threadIdx.x & 31) == 0) { sb[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = best_i; }
+  __shared__ unsigned long long sk[8];
+  if ((threadIdx.x & 31) == 0) sk[threadIdx.x >> 5] = key;
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int i = 1; i < 8; ++i)
-      if (sb[i] > best || (sb[i] == best && si[i] < best_i)) { best = sb[i]; best_i = si[i]; }
-    out[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
+    for (int i = 1; i < 8; ++i) key = sk[i] > key ? sk[i] : key;
+    atomicMax(keys + blockIdx.x, key);
+  }
+}
+
+__global__ void argmax_finish_kernel(int64_t* __restrict__ out, int B) {
+  b2::pdl_launch_dependents();
+  b2::pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < B) {
+    const unsigned long long key = static_cast<unsigned long long>(out[i]);
+    out[i] = key == 0ull ? 0 : static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(key & 0xFFFFFFFFull));
   }
 }
 
@@ -575,7 +595,16 @@ int b2_argmax(const void* logits, int64_t ld, int B, int V, int64_t* out, void* 
   if (B < 0 || V <= 0 || ld % 8 != 0 || ld < V) return B2_ERR_ARG;
   if (B == 0) return B2_OK;
   if (!logits || !out || !aligned16(logits)) return B2_ERR_ARG;
-  B2_CUDA(b2_launch(argmax_kernel, dim3(B), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(logits), ld, V, out));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // enough blocks per row to fill the GPU, at least 4096 columns each
+  int parts = std::max(1, std::min(32, 592 / std::max(1, B)));
+  int cols = ((V + parts - 1) / parts + 7) / 8 * 8;
+  if (cols < 4096) cols = 4096;
+  parts = (V + cols - 1) / cols;
+  B2_CUDA(cudaMemsetAsync(out, 0, static_cast<size_t>(B) * sizeof(int64_t), s));  // key 0 loses against every real key
+  B2_CUDA(b2_launch(argmax_partial_kernel, dim3(B, parts), dim3(256), 0, s, static_cast<const uint16_t*>(logits), ld, V, cols,
+                    reinterpret_cast<unsigned long long*>(out)));
+  B2_CUDA(b2_launch(argmax_finish_kernel, dim3((B + 127) / 128), dim3(128), 0, s, out, B));
   return B2_OK;
 }
 

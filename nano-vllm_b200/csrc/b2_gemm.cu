@@ -122,37 +122,59 @@ struct Seg {
 struct Work {
   int n_units, u_begin, KB, G, cta;
   bool rr;
+  // stream-K: the range [u_begin, u_begin + n_units) is walked as a list of pieces; piece_start[] are global
+  // unit indices, piece_end[] local indices (cumulative lengths).  Today there is one piece: the range front to
+  // back.  (Walking the partial tiles at both ends first, so that the launch ends on a whole tile's plain
+  // store, was measured 1 us slower on the 192-tile decode GEMM and is not used.)
+  int piece_start[3], piece_end[3];
 };
+__device__ __forceinline__ void plan_pieces(Work& w) {
+  w.piece_start[0] = w.piece_start[1] = w.piece_start[2] = w.u_begin;
+  w.piece_end[0] = w.piece_end[1] = w.piece_end[2] = w.n_units;
+}
+__device__ __forceinline__ int piece_of(const Work& w, int i) { return i < w.piece_end[0] ? 0 : (i < w.piece_end[1] ? 1 : 2); }
 __device__ __forceinline__ void unit_at(const Work& w, int i, int& tile, int& kb) {
   if (w.rr) {
     const int j = i / w.KB;
     kb = i - j * w.KB;
     tile = w.cta + j * w.G;
   } else {
-    const int u = w.u_begin + i;
+    const int p = piece_of(w, i);
+    const int u = w.piece_start[p] + (i - (p == 0 ? 0 : w.piece_end[p - 1]));
     tile = u / w.KB;
     kb = u - tile * w.KB;
   }
 }
-// Walks the units one by one without dividing: the TMA producer is a single thread whose instruction
-// stream competes with an epilogue warp for issue slots, so its per-K-block arithmetic has to stay short.
+// Walks the units one by one without dividing (except once per piece): the TMA producer is a single thread
+// whose instruction stream competes with an epilogue warp for issue slots, so its per-K-block arithmetic has
+// to stay short.
 struct Cursor {
-  int tile, kb, tp, tq;
+  int tile, kb, tp, tq, i, next_jump;
 };
-__device__ __forceinline__ Cursor cursor_begin(const Work& w, int tilesQ) {
-  Cursor c;
-  unit_at(w, 0, c.tile, c.kb);
+__device__ __forceinline__ void cursor_seek(const Work& w, int tilesQ, Cursor& c) {
+  unit_at(w, c.i, c.tile, c.kb);
   c.tp = c.tile / tilesQ;
   c.tq = c.tile - c.tp * tilesQ;
+  c.next_jump = w.rr ? w.n_units : w.piece_end[piece_of(w, c.i)];
+}
+__device__ __forceinline__ Cursor cursor_begin(const Work& w, int tilesQ) {
+  Cursor c;
+  c.i = 0;
+  if (w.n_units > 0) cursor_seek(w, tilesQ, c);
   return c;
 }
 __device__ __forceinline__ void cursor_next(const Work& w, int tilesQ, Cursor& c) {
+  if (++c.i >= w.n_units) return;
+  if (c.i == c.next_jump) {  // next piece starts somewhere else
+    cursor_seek(w, tilesQ, c);
+    return;
+  }
   if (++c.kb == w.KB) {
     c.kb = 0;
     const int step = w.rr ? w.G : 1;
     c.tile += step;
     c.tq += step;
-    while (c.tq >= tilesQ) {  // at most a few turns: step <= G, and tilesQ is 1 whenever G is large relative to it
+    while (c.tq >= tilesQ) {
       c.tq -= tilesQ;
       ++c.tp;
     }
@@ -162,7 +184,8 @@ __device__ __forceinline__ bool next_seg(const Work& w, int& i, Seg& s) {
   if (i >= w.n_units) return false;
   int tile, kb;
   unit_at(w, i, tile, kb);
-  const int len = min(w.KB - kb, w.n_units - i);
+  const int limit = w.rr ? w.n_units : w.piece_end[piece_of(w, i)];
+  const int len = min(w.KB - kb, limit - i);
   s.tile = tile;
   s.kb0 = kb;
   s.kb1 = kb + len;
@@ -588,6 +611,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   if (!has_gemm) work.n_units = 0;
   else if (work.rr) work.n_units = ((tiles - cta + a.gemm_ctas - 1) / a.gemm_ctas) * KB;
   else work.n_units = part.u0(cta + 1) - work.u_begin;
+  plan_pieces(work);
 
   if (threadIdx.x == 0) {
     stamp(a, 7);

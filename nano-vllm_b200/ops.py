@@ -94,6 +94,9 @@ def gemm_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor) -> torch.Tensor:
 def _two_shot_min_tokens(world: int) -> int:
     """From this many tokens on the two-shot kernel is used.  One-shot pushes (world-1) copies of the partial,
     two-shot 2 (world-1)/world: the same at world 2, 4.6x less at world 8."""
+    forced = os.environ.get("B2_TWO_SHOT_MIN_TOKENS")  # measurement switch
+    if forced:
+        return int(forced)
     return 257 if world <= 2 else 128
 
 

@@ -35,14 +35,20 @@ def _worker(rank: int, world: int, port: int):
         results = []
         for i, (m, k, n) in enumerate(shapes):
             xs, ws, residual, norm_w = O.rowpar_case(m, k, n, world, seed=100 + i)
-            out = ops.rowpar_fused(xs[rank].to(dev), ws[rank].to(dev), None, residual.to(dev), norm_w.to(dev), 1e-6)
-            results.append((out, xs, ws, residual, norm_w, (m, k, n)))
+            normed, new_res = ops.rowpar_fused(xs[rank].to(dev), ws[rank].to(dev), None, residual.to(dev), norm_w.to(dev), 1e-6)
+            # (the two-shot form returns a view of a buffer the next two-shot call reuses: keep a copy)
+            results.append(((normed.clone(), new_res), xs, ws, residual, norm_w, (m, k, n)))
         torch.cuda.synchronize()
         rt.check_status()
         for (normed, new_res), xs, ws, residual, norm_w, shp in results:
             exact_n, exact_s = O.fused_row_parallel_norm_exact(xs, ws, residual, norm_w, 1e-6)
-            assert_close_bf16(new_res, exact_s, f"rank {rank} residual {shp}")
             assert_close_bf16(normed, exact_n, f"rank {rank} normed {shp}")
+            if shp[2] == rt.hidden and shp[0] >= ops._two_shot_min_tokens(world):
+                # two-shot form: the residual stays with the ranks that own the rows (16-row blocks, round-robin)
+                mine = (torch.arange(shp[0]) // 16) % world == rank
+                assert_close_bf16(new_res.cpu()[mine], exact_s[mine], f"rank {rank} residual (owned rows) {shp}")
+                continue
+            assert_close_bf16(new_res, exact_s, f"rank {rank} residual {shp}")
             # the reference rounds the all-reduced sum to bf16 before the residual add; the fused kernel keeps
             # it in fp32, so the two differ by at most that one rounding (2^-8 relative to the summed value)
             ref_n, ref_s = O.fused_row_parallel_norm(xs, ws, residual, norm_w, 1e-6)
