@@ -29,7 +29,7 @@ def _worker(rank: int, world: int, port: int):
     vocab = 4096 * world
     # every rank computes the CPU oracle of every case: keep the cases small when there are many ranks
     torch.set_num_threads(max(1, (os.cpu_count() or 8) // world))
-    big = world <= 2
+    big = world <= 2 and os.environ.get("B2_TEST_SMALL_CASES") != "1"
     H = 5120 if big else 1024
     rt = init_runtime(max_tokens=4096, hidden=H, oneshot_tokens=512, vocab=vocab, max_seqs=64)
     try:
@@ -38,7 +38,7 @@ def _worker(rank: int, world: int, port: int):
             shapes = [(64, 4096, 4096), (1, 2048, 1024), (8, 8192, H), (64, 12288, 4096), (200, 1024, H), (512, 2048, 1024),
                       (700, 1024, 2048), (64, 4096, 4096)]
         else:
-            shapes = [(64, 2048, 1024), (1, 1024, 1024), (8, 2048, H), (200, 1024, H), (512, 1024, 1024), (64, 1024, 2048)]
+            shapes = [(64, 2048, 1024), (1, 1024, 1024), (8, 2048, H), (200, 1024, H), (512, 1024, 1024), (64, 1024, 512)]
         results = []
         for i, (m, k, n) in enumerate(shapes):
             xs, ws, residual, norm_w = O.rowpar_case(m, k, n, world, seed=100 + i)

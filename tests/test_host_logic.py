@@ -135,3 +135,63 @@ def test_layers_fail_loudly_without_cuda(pkg):
     from nanovllm_b200.runtime import TPRuntime
     with pytest.raises(RuntimeError, match="CUDA"):
         TPRuntime(0, 1, 0, 16, 64)
+
+
+# ---- two-shot ownership of token rows (owner_of / owned_rows in csrc/b2_gemm.cu) ----
+def owner_of(token, world):
+    b = token >> 4
+    return b % world, ((b // world) << 4) + (token & 15)
+
+
+def owned_rows(m, world, rank):
+    blocks = (m + 15) >> 4
+    mine = (blocks - rank + world - 1) // world
+    if mine <= 0:
+        return 0
+    last_block = rank + (mine - 1) * world
+    last_rows = m - (last_block << 4) if last_block == blocks - 1 else 16
+    return (mine - 1) * 16 + last_rows
+
+
+@pytest.mark.parametrize("m", [1, 15, 16, 17, 128, 200, 300, 777, 1024, 4096, 16384])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_two_shot_row_ownership(m, world):
+    per_rank = {r: [] for r in range(world)}
+    for t in range(m):
+        o, l = owner_of(t, world)
+        per_rank[o].append(l)
+    for r in range(world):
+        n = owned_rows(m, world, r)
+        # the owner's local rows are exactly 0 .. n-1, each once: the reduce phase walks them as a dense range
+        assert sorted(per_rank[r]) == list(range(n)), (m, world, r)
+        # and the reduce phase's inverse map (local row -> token) lands on this rank's tokens
+        for row in range(n):
+            token = (((row >> 4) * world + r) << 4) + (row & 15)
+            assert token < m and owner_of(token, world) == (r, row)
+    assert sum(owned_rows(m, world, r) for r in range(world)) == m
+    # the inbox is sized for the rank that owns most
+    max_rows = ((16384 + 15) // 16 + world - 1) // world * 16
+    assert max(owned_rows(min(m, 16384), world, r) for r in range(world)) <= max_rows
+
+
+# ---- cluster kernel: 4-column groups of the accumulator dealt round-robin to the S CTAs of a cluster ----
+@pytest.mark.parametrize("bn", [32, 64])
+@pytest.mark.parametrize("s_", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_cluster_group_distribution(bn, s_):
+    groups = bn // 4
+    gl = (groups + s_ - 1) // s_
+    owned = {}
+    for crank in range(s_):
+        for l in range(gl):
+            g = l * s_ + crank
+            if g < groups:
+                assert g not in owned
+                owned[g] = (crank, l)
+    assert sorted(owned) == list(range(groups))            # every group has exactly one owner
+    assert s_ * gl <= groups + 8                            # the receive buffer [source][local group] is large enough
+    for g, (crank, l) in owned.items():                     # sender-side rule: owner = g % S, local index = g / S
+        assert (g % s_, g // s_) == (crank, l)
+    # tokens of the rows a CTA stores: local token lt = l*4 + j  <->  token (l*S + crank)*4 + j
+    tokens = sorted((((lt >> 2) * s_ + crank) << 2) + (lt & 3) for crank in range(s_) for lt in range(gl * 4)
+                    if (lt >> 2) * s_ + crank < groups)
+    assert tokens == list(range(bn))
