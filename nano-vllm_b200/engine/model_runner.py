@@ -194,12 +194,52 @@ class ModelRunner:
         self.graphs[bs].replay()
         return self.model.compute_logits(gv["outputs"][:n])
 
+    def _decode_staging(self):
+        """Pinned host mirrors of the graphs' input buffers, allocated once: a decode step fills them with
+        numpy and issues one asynchronous copy per buffer straight into the graph's inputs (no per-step pinned
+        allocations, no device-to-device staging copies)."""
+        if getattr(self, "_stage", None) is None:
+            gv = self.graph_vars
+            self._stage = {k: torch.zeros(gv[k].shape, dtype=gv[k].dtype, pin_memory=True) for k in
+                           ("input_ids", "positions", "slot_mapping", "context_lens", "block_tables")}
+            self._stage_np = {k: v.numpy() for k, v in self._stage.items()}
+        return self._stage, self._stage_np
+
+    @torch.inference_mode()
+    def _decode_graph_step(self, seqs: list[Seq]):
+        """prepare_decode + the graph replay of run_model in one go, for batches a captured graph covers."""
+        n = len(seqs)
+        bs = next(b for b in self.graph_bs if b >= n)
+        stage, np_ = self._decode_staging()
+        blk = self.block_size
+        lens = [len(s) for s in seqs]
+        np_["input_ids"][:n] = [s.token_ids[-1] for s in seqs]
+        np_["positions"][:n] = [l - 1 for l in lens]
+        np_["context_lens"][:n] = lens
+        np_["context_lens"][n:bs] = 0          # padded rows attend to nothing ...
+        np_["slot_mapping"][:n] = [s.block_table[(l - 1) // blk] * blk + (l - 1) % blk for s, l in zip(seqs, lens)]
+        np_["slot_mapping"][n:bs] = -1         # ... and store nothing
+        width = max(len(s.block_table) for s in seqs)
+        bt = np_["block_tables"]
+        for i, s in enumerate(seqs):
+            bt[i, :len(s.block_table)] = s.block_table
+        gv = self.graph_vars
+        for k in ("input_ids", "positions", "slot_mapping", "context_lens"):
+            gv[k][:bs].copy_(stage[k][:bs], non_blocking=True)
+        gv["block_tables"][:n, :width].copy_(stage["block_tables"][:n, :width], non_blocking=True)
+        self.graphs[bs].replay()
+        set_context(False)  # the LM head only needs to know this is not a prefill step
+        return self.model.compute_logits(gv["outputs"][:n])
+
     @torch.inference_mode()
     def step(self, seqs: list[Seq], is_prefill: bool, temperatures: list[float] | None = None, num_new: list[int] | None = None):
         """One forward pass + sampling on rank 0; the chosen token ids are
         returned on every rank.  temperatures=None means greedy (argmax)."""
-        ids, pos = self.prepare_prefill(seqs, num_new) if is_prefill else self.prepare_decode(seqs)
-        logits = self.run_model(ids, pos, is_prefill)
+        if not is_prefill and not self.enforce_eager and len(seqs) <= self.graph_bs[-1]:
+            logits = self._decode_graph_step(seqs)
+        else:
+            ids, pos = self.prepare_prefill(seqs, num_new) if is_prefill else self.prepare_decode(seqs)
+            logits = self.run_model(ids, pos, is_prefill)
         picked = torch.zeros(len(seqs), dtype=torch.int64, device=self.device)
         if self.rank == 0:
             if temperatures is None:
