@@ -37,9 +37,9 @@ METRIC = "qwen3_8b_decode_tokens_per_s"
 BATCH, PROMPT_LEN = 64, 1024
 SHAPE_8B = dict(hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128, intermediate=12288, n_layers=36, vocab=151936)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# dram__bytes_read.sum + dram__bytes_write.sum of one gate_up GEMM launch at TP=1 from the committed ncu summary
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate_up (+SiLU*mul) launch at TP=1 from the committed ncu summary
 # (profiles/), per tensor-parallel size; None = not captured
-NCU_TRAFFIC_BYTES = {1: 208.6e6}
+NCU_TRAFFIC_BYTES = {1: 212.9e6}
 
 
 def workload(tp: int) -> dict:
@@ -230,13 +230,14 @@ def run_b200(args) -> None:
     layers = runner.model.model.layers
     x = torch.randn(BATCH, SHAPE_8B["hidden"], device=dev).bfloat16()
     n_local = 2 * SHAPE_8B["intermediate"] // world
+    paired = [l.mlp.gate_up_proj.paired_weight() for l in layers]  # what the decoder layer launches: gate_up with SiLU*mul in the epilogue
     # one CUDA graph holds one launch per layer's weight (36 x 201 MB / TP: never L2-resident), so the host is out of the loop
     from nanovllm_b200.rowpar_microbench import time_in_graph
     with torch.inference_mode():
-        k_us = time_in_graph(lambda i: ops.gemm(x, layers[i % len(layers)].mlp.gate_up_proj.weight), len(layers), 6 * len(layers))
-    alg_bytes = 2.0 * (BATCH * SHAPE_8B["hidden"] + n_local * SHAPE_8B["hidden"] + BATCH * n_local)
+        k_us = time_in_graph(lambda i: ops.gemm_silu_mul(x, paired[i % len(layers)]), len(layers), 6 * len(layers))
+    alg_bytes = 2.0 * (BATCH * SHAPE_8B["hidden"] + n_local * SHAPE_8B["hidden"] + BATCH * n_local // 2)
     achieved = alg_bytes / (k_us * 1e-6) / 1e9
-    roofline = {"bound": "hbm", "kernel": f"gemm_kernel<BN=64,SWAP> gate_up_proj M={BATCH} N={n_local} K={SHAPE_8B['hidden']}", "achieved": achieved,
+    roofline = {"bound": "hbm", "kernel": f"{'gemm_kernel<64,SWAP,STORE> (stream-K)' if n_local // 128 > 148 else 'gemm_cluster_kernel<64,STORE>'} gate_up_proj + SiLU*mul, M={BATCH} N={n_local} K={SHAPE_8B['hidden']}", "achieved": achieved,
                 "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_kind": pk_kind + " (burst copy bandwidth)",
                 "us_per_launch": k_us, "algorithmic_bytes": alg_bytes, "traffic": NCU_TRAFFIC_BYTES.get(world)}
     # the whole step against the HBM bound: weights of the rank + KV read at the mean context length
