@@ -87,8 +87,11 @@ extern "C" {
 const char* b2_last_error(void) { return g_last_error; }
 int64_t b2_launch_count(void) { return g_launches.load(); }
 
+static int ctx_init(b2_ctx* c);
+
 int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
   if (cfg == nullptr || out == nullptr) return B2_ERR_ARG;
+  *out = nullptr;
   if (cfg->world < 1 || cfg->world > B2_MAX_WORLD || cfg->rank < 0 || cfg->rank >= cfg->world) return B2_ERR_ARG;
   if (cfg->max_tokens < 1 || cfg->hidden < 8 || cfg->hidden % 8 != 0) return B2_ERR_ARG;
   b2_ctx* c = new (std::nothrow) b2_ctx();
@@ -98,6 +101,17 @@ int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
   if (c->cfg.oneshot_tokens <= 0) c->cfg.oneshot_tokens = 1024;
   if (c->cfg.oneshot_tokens > c->cfg.max_tokens) c->cfg.oneshot_tokens = c->cfg.max_tokens;
   if (c->cfg.timeout_ms <= 0) c->cfg.timeout_ms = 5000;
+  const int rc = ctx_init(c);
+  if (rc != B2_OK) {
+    b2_ctx_destroy(c);  // frees whatever was allocated before the failing call; the error text stays
+    return rc;
+  }
+  *out = c;
+  return B2_OK;
+}
+
+static int ctx_init(b2_ctx* c) {
+  const b2_config* cfg = &c->cfg;
   B2_CUDA(cudaSetDevice(cfg->device));
   cudaDeviceProp prop;
   B2_CUDA(cudaGetDeviceProperties(&prop, cfg->device));
@@ -156,7 +170,6 @@ int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
   B2_CUDA(cudaMemset(c->trace, 0, static_cast<size_t>(c->num_sms) * 16 * sizeof(unsigned long long)));
   c->trace_on = false;
   B2_CUDA(cudaDeviceSynchronize());
-  *out = c;
   return B2_OK;
 }
 
@@ -196,7 +209,8 @@ int b2_ctx_destroy(b2_ctx* c) {
   cudaFree(c->dstate);
   cudaFree(c->trace);
   if (c->gather_rows) cudaFree(c->gather_rows);
-  cudaFreeHost(c->status_host);
+  if (c->status_host) cudaFreeHost(c->status_host);
+  cudaGetLastError();  // a failed free of a never-made allocation is not an error of the caller
   delete c;
   return B2_OK;
 }

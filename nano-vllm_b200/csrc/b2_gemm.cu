@@ -1,36 +1,51 @@
-// bf16 GEMM for sm_100a: TMA-fed shared-memory pipeline, tcgen05.mma with fp32
-// accumulators in tensor memory, warp-specialised (1 TMA warp, 1 MMA warp,
-// 4 epilogue warps), persistent over a stream-K partition of the work.
+// bf16 GEMMs for sm_100a: TMA-fed shared-memory pipeline, tcgen05.mma with fp32
+// accumulators in tensor memory, warp-specialised (1 TMA thread, 1 MMA thread,
+// 4 epilogue warps).  Two kernels share the operand convention and epilogues:
+//
+//   gemm_kernel          persistent over a stream-K partition of the work (any size)
+//   gemm_cluster_kernel  one thread-block cluster per output tile, K split over the
+//                        cluster, parts combined through distributed shared memory
+//                        (decode sizes: at most 64 tokens and one wave of tiles)
 //
 // D[p, q] = sum_k P[p, k] * Q[q, k]; both operands are K-major (row-major with
 // K contiguous).  P tiles have 128 rows (the MMA M dimension = 128 TMEM
 // lanes), Q tiles have BN rows (the MMA N dimension = BN TMEM columns).
-//   SWAP = false: P = activations [tokens, K], Q = weights [features, K]
-//   SWAP = true : P = weights, Q = activations (few tokens: the 128-row side
-//                 is filled by weight rows, so no tensor-core work is wasted
-//                 and every SM streams a distinct slab of the weight matrix)
+//   SWAP = false ("token-row" layout): P = activations [tokens, K], Q = weights
+//   SWAP = true ("feature-lane" layout): P = weights, Q = activations (few tokens:
+//                 the 128-row side is filled by weight rows, so no tensor-core work
+//                 is wasted and every SM streams a distinct slab of the weights)
 //
-// Work unit = one 64-wide K block of one output tile.  The units are dealt in
-// contiguous ranges to the CTAs; a tile whose K range is shared by several
-// CTAs is combined in an fp32 accumulation slot in L2 (vector red.add): the
-// CTA that arrives last at the tile's counter reads the sum, re-zeroes the
-// slot and writes the output.  Nobody waits for anybody.
+// Stream-K: work unit = one 64-wide K block of one output tile.  The units are
+// dealt in contiguous ranges to the CTAs; a tile whose K range is shared by
+// several CTAs is combined in an fp32 accumulation slot in L2 (vector red.add):
+// the CTA that arrives last at the tile's counter reads the sum, re-zeroes the
+// slot and writes the output.  Nobody waits for anybody.  Up to 4 accumulators
+// in tensor memory let a tile's epilogue overlap the next tile's MMAs.
 //
-// EPI_PUSH2: the two-shot form for many tokens.  Token rows are dealt in equal
-// contiguous blocks to the ranks.  The epilogue stores each partial row only
-// into the inbox of the rank that owns it; the owner sums the partials of its
-// rows, adds the residual, normalises, and stores the finished row into every
-// rank's output buffer (symmetric memory), then adds the number of rows it
-// finished to each peer's arrival counter.  A launch ends when its rank has
-// received all rows it does not own.  NVLink carries 2 (tp-1)/tp M N 2 bytes
-// per rank, the minimum for an all-reduce.
+// Epilogues:
+//   EPI_STORE  C = D (+ bias); optionally SiLU(gate) * up on interleaved
+//              (gate, up) feature pairs; in the cluster kernel optionally the
+//              per-head work of the qkv projection (q/k RMSNorm, RoPE, KV scatter).
+//   EPI_PUSH   the fused row-parallel path, one-shot.  The epilogue rounds the
+//              tile to bf16 and stores it into the inbox of every rank (its own
+//              and, over NVLink, its peers'); then every CTA turns to whole rows
+//              of the inbox: it sums the partials of all ranks, adds the residual,
+//              applies RMSNorm and writes the results.  The inbox is data-as-flag:
+//              a slot holds the sentinel until the value lands, and the reader puts
+//              the sentinel back after consuming it.
+//   EPI_PUSH2  the two-shot form for many tokens.  Token rows are dealt to the
+//              ranks in 16-row blocks, round-robin.  The epilogue stores each
+//              partial row only into the inbox of the rank that owns it; the owner
+//              sums the partials of its rows, adds the residual, normalises, and
+//              stores the finished row into every rank's output buffer (symmetric
+//              memory), then adds the number of rows it finished to each peer's
+//              arrival counter.  A launch ends when its rank has received all rows
+//              it does not own.  NVLink carries 2 (tp-1)/tp M N 2 bytes per rank,
+//              the minimum for an all-reduce.
 //
-// EPI_PUSH: the fused row-parallel path.  The epilogue rounds the tile to bf16
-// and stores it into the inbox of every rank (its own and, over NVLink, its
-// peers'); then every CTA turns to whole rows of the inbox: it sums the
-// partials of all ranks, adds the residual, applies RMSNorm and writes the
-// results.  The inbox is data-as-flag: a slot holds the sentinel until the
-// value lands, and the reader puts the sentinel back after consuming it.
+// Every kernel is launched with the programmatic-dependent-launch attribute:
+// set-up and the first ring of weight tiles are issued before
+// griddepcontrol.wait, i.e. while the previous kernel of the stream is ending.
 #include <algorithm>
 #include <cstdlib>
 #include <mutex>
