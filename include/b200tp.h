@@ -284,6 +284,46 @@ int b2_qk_norm_rope_store(void* qkv, int64_t ld_qkv, int M, int nq, int nkv, int
  * The reference's Sampler (nanovllm/layers/sampler.py:7-12) at temperature -> 0. */
 int b2_argmax(const void* logits, int64_t ld, int B, int V, int64_t* out, void* stream);
 
+/* ---- the launch planner as data (no counterpart in the reference; no CUDA
+ *      call, usable without a GPU) -------------------------------------------
+ * How the GEMM entry points would split a problem over the device: which
+ * operand layout and tile width, how many CTAs share the K blocks, and which
+ * kernel runs.  The host tests use it to check that every K block of every
+ * output tile is computed exactly once for any shape. */
+typedef struct b2_gemm_plan {
+  int swap;          /* 1: weights on the 128-row side of the MMA (M <= 256)     */
+  int bn;            /* rows of the other operand's tile                         */
+  int tiles_p, tiles_q, kblocks; /* tile grid and 64-wide K blocks per tile      */
+  int gemm_ctas;     /* CTAs that share the GEMM work                            */
+  int round_robin;   /* 1: whole tiles dealt round-robin (no split tiles)        */
+  int grid;          /* CTAs launched                                            */
+  int cluster_split; /* > 0: cluster kernel, K split this many ways; 0: stream-K */
+} b2_gemm_plan;
+
+/* epilogue: 0 = b2_gemm / b2_lm_head / b2_gemm_silu_mul / b2_qkv_fused,
+ * 1 = b2_rowpar_fused, 2 = b2_rowpar_fused_twoshot.  resident_clusters: NULL
+ * (cluster kernel not considered) or int[18]: entry [S] for 32-token tiles and
+ * [9 + S] for 64-token tiles = clusters of S CTAs the device holds at once
+ * (on a GPU the library asks the occupancy calculator). */
+int b2_plan_gemm(int epilogue, int M, int N, int K, int num_sms, const int* resident_clusters, b2_gemm_plan* plan);
+
+/* The K blocks CTA `cta` computes under `plan`, in order, as triples
+ * (tile, k_block, starts_segment) written to units[3 * cap].  Returns their
+ * number (which may exceed cap), or a negative error code if the producer's
+ * and the consumers' walks over the plan disagree. */
+int b2_plan_cta_units(const b2_gemm_plan* plan, int cta, int* units, int cap);
+
+/* The CTAs that hold K blocks of output tile `tile`: first_cta .. last_cta.
+ * The stream-K kernel's "last arriver stores" counter expects exactly
+ * last - first + 1 arrivals. */
+int b2_plan_tile_contributors(const b2_gemm_plan* plan, int tile, int* first_cta, int* last_cta);
+
+/* Two-shot row ownership: the rank that reduces token row `token` (blocks of
+ * 16 rows dealt round-robin) and the row's index in that rank's inbox; the
+ * number of rows of an M-row call that `rank` owns.  Negative on bad input. */
+int b2_row_owner(int token, int world, int* local_row);
+int b2_owned_rows(int M, int world, int rank);
+
 #ifdef __cplusplus
 }
 #endif

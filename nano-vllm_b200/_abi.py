@@ -37,6 +37,11 @@ class B2Error(RuntimeError):
     pass
 
 
+class GemmPlan(C.Structure):
+    """b2_gemm_plan: what the launch planner decides for one GEMM (host arithmetic only)."""
+    _fields_ = [(n, C.c_int) for n in ("swap", "bn", "tiles_p", "tiles_q", "kblocks", "gemm_ctas", "round_robin", "grid", "cluster_split")]
+
+
 _p, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
 
 SIGNATURES = {
@@ -63,6 +68,12 @@ SIGNATURES = {
     "b2_argmax": [_p, _i64, _i, _i, _p, _p],
     "b2_broadcast_tokens": [_p, _p, _i, _p],
     "b2_advance_decode": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _p],
+    # the planner as data: no CUDA call, usable without a GPU
+    "b2_plan_gemm": [_i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(GemmPlan)],
+    "b2_plan_cta_units": [C.POINTER(GemmPlan), _i, C.POINTER(_i), _i],
+    "b2_plan_tile_contributors": [C.POINTER(GemmPlan), _i, C.POINTER(_i), C.POINTER(_i)],
+    "b2_row_owner": [_i, _i, C.POINTER(_i)],
+    "b2_owned_rows": [_i, _i, _i],
 }
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)

@@ -137,18 +137,19 @@ struct Seg {
 struct Work {
   int n_units, u_begin, KB, G, cta;
   bool rr;
+  Partition part;  // stream-K: which CTA holds which unit
   // stream-K: the range [u_begin, u_begin + n_units) is walked as a list of pieces; piece_start[] are global
   // unit indices, piece_end[] local indices (cumulative lengths).  Today there is one piece: the range front to
   // back.  (Walking the partial tiles at both ends first, so that the launch ends on a whole tile's plain
   // store, was measured 1 us slower on the 192-tile decode GEMM and is not used.)
   int piece_start[3], piece_end[3];
 };
-__device__ __forceinline__ void plan_pieces(Work& w) {
+__host__ __device__ __forceinline__ void plan_pieces(Work& w) {
   w.piece_start[0] = w.piece_start[1] = w.piece_start[2] = w.u_begin;
   w.piece_end[0] = w.piece_end[1] = w.piece_end[2] = w.n_units;
 }
-__device__ __forceinline__ int piece_of(const Work& w, int i) { return i < w.piece_end[0] ? 0 : (i < w.piece_end[1] ? 1 : 2); }
-__device__ __forceinline__ void unit_at(const Work& w, int i, int& tile, int& kb) {
+__host__ __device__ __forceinline__ int piece_of(const Work& w, int i) { return i < w.piece_end[0] ? 0 : (i < w.piece_end[1] ? 1 : 2); }
+__host__ __device__ __forceinline__ void unit_at(const Work& w, int i, int& tile, int& kb) {
   if (w.rr) {
     const int j = i / w.KB;
     kb = i - j * w.KB;
@@ -166,19 +167,19 @@ __device__ __forceinline__ void unit_at(const Work& w, int i, int& tile, int& kb
 struct Cursor {
   int tile, kb, tp, tq, i, next_jump;
 };
-__device__ __forceinline__ void cursor_seek(const Work& w, int tilesQ, Cursor& c) {
+__host__ __device__ __forceinline__ void cursor_seek(const Work& w, int tilesQ, Cursor& c) {
   unit_at(w, c.i, c.tile, c.kb);
   c.tp = c.tile / tilesQ;
   c.tq = c.tile - c.tp * tilesQ;
   c.next_jump = w.rr ? w.n_units : w.piece_end[piece_of(w, c.i)];
 }
-__device__ __forceinline__ Cursor cursor_begin(const Work& w, int tilesQ) {
+__host__ __device__ __forceinline__ Cursor cursor_begin(const Work& w, int tilesQ) {
   Cursor c;
   c.i = 0;
   if (w.n_units > 0) cursor_seek(w, tilesQ, c);
   return c;
 }
-__device__ __forceinline__ void cursor_next(const Work& w, int tilesQ, Cursor& c) {
+__host__ __device__ __forceinline__ void cursor_next(const Work& w, int tilesQ, Cursor& c) {
   if (++c.i >= w.n_units) return;
   if (c.i == c.next_jump) {  // next piece starts somewhere else
     cursor_seek(w, tilesQ, c);
@@ -195,12 +196,12 @@ __device__ __forceinline__ void cursor_next(const Work& w, int tilesQ, Cursor& c
     }
   }
 }
-__device__ __forceinline__ bool next_seg(const Work& w, int& i, Seg& s) {
+__host__ __device__ __forceinline__ bool next_seg(const Work& w, int& i, Seg& s) {
   if (i >= w.n_units) return false;
   int tile, kb;
   unit_at(w, i, tile, kb);
   const int limit = w.rr ? w.n_units : w.piece_end[piece_of(w, i)];
-  const int len = min(w.KB - kb, limit - i);
+  const int len = (w.KB - kb) < (limit - i) ? (w.KB - kb) : (limit - i);
   s.tile = tile;
   s.kb0 = kb;
   s.kb1 = kb + len;
@@ -208,9 +209,29 @@ __device__ __forceinline__ bool next_seg(const Work& w, int& i, Seg& s) {
   return true;
 }
 
+// The share of CTA `cta` when `tiles` tiles of KB K blocks are dealt to the first G CTAs of the grid.
+__host__ __device__ __forceinline__ Work make_work(int cta, int G, int tiles, int KB, bool rr) {
+  Work w;
+  const int U = tiles * KB;
+  w.part.base = U / G;
+  w.part.rem = U % G;
+  const Partition& part = w.part;
+  w.KB = KB;
+  w.G = G;
+  w.cta = cta;
+  w.rr = rr;
+  const bool has = cta < G;
+  w.u_begin = has ? part.u0(cta) : 0;
+  if (!has) w.n_units = 0;
+  else if (rr) w.n_units = ((tiles - cta + G - 1) / G) * KB;
+  else w.n_units = part.u0(cta + 1) - w.u_begin;
+  plan_pieces(w);
+  return w;
+}
+
 // Two-shot ownership of token rows: blocks of 16 rows are dealt round-robin to the ranks.
 constexpr int OWN_SHIFT = 4, OWN_ROWS = 1 << OWN_SHIFT;
-__device__ __forceinline__ int owner_of(int token, int world, int& local_row) {
+__host__ __device__ __forceinline__ int owner_of(int token, int world, int& local_row) {
   const int b = token >> OWN_SHIFT;
   local_row = ((b / world) << OWN_SHIFT) + (token & (OWN_ROWS - 1));
   return b % world;
@@ -612,21 +633,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   const int cta = blockIdx.x;
   const int KB = a.kblocks;
   const int tiles = a.tilesP * a.tilesQ;
-  const int U = tiles * KB;
   const bool has_gemm = cta < a.gemm_ctas;
-  Partition part;
-  part.base = U / a.gemm_ctas;
-  part.rem = U % a.gemm_ctas;
-  Work work;
-  work.KB = KB;
-  work.G = a.gemm_ctas;
-  work.cta = cta;
-  work.rr = a.round_robin != 0;
-  work.u_begin = has_gemm ? part.u0(cta) : 0;
-  if (!has_gemm) work.n_units = 0;
-  else if (work.rr) work.n_units = ((tiles - cta + a.gemm_ctas - 1) / a.gemm_ctas) * KB;
-  else work.n_units = part.u0(cta + 1) - work.u_begin;
-  plan_pieces(work);
+  const Work work = make_work(cta, a.gemm_ctas, tiles, KB, a.round_robin != 0);
 
   if (threadIdx.x == 0) {
     stamp(a, 7);
@@ -768,7 +776,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
           // the contributor that arrives last at the tile's counter reads the sum once, puts the slot
           // back to zero for the next launch, and writes the output.  The slot of a split tile is indexed
           // by its first contributor, which is unique among split tiles.
-          const int c_first = part.cta_of(s.tile * KB), c_last = part.cta_of(s.tile * KB + KB - 1);
+          const int c_first = work.part.cta_of(s.tile * KB), c_last = work.part.cta_of(s.tile * KB + KB - 1);
           float* slot = a.ws + (static_cast<size_t>(c_first) * 4 + q) * (BN * 32) + lane * 4;
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
@@ -1214,60 +1222,105 @@ bool cluster_path_enabled() {
   return on;
 }
 
+// What launch_gemm decides for one problem, as data (the CPU tests read it through b2_plan_gemm).
+struct GemmPlan {
+  int swap;           // 1 = feature-lane layout (weights on the 128-row side)
+  int bn;             // rows of the Q tile
+  int tilesP, tilesQ, kblocks;
+  int gemm_ctas;      // CTAs that share the GEMM units
+  int round_robin;    // stream-K kernel: whole tiles dealt round-robin
+  int grid;           // CTAs launched
+  int cluster_split;  // > 0: cluster kernel with this K split; 0: stream-K kernel
+};
+
+int twoshot_reducers() {
+  // B2_TWOSHOT_REDUCERS=n sets n CTAs aside that only reduce, following the GEMM's sweep over the rows, so
+  // that the second half of the NVLink traffic overlaps the tensor-core work.  Default 0: every CTA reduces
+  // after its GEMM work (SM time, not NVLink, bounds most shapes, and then setting CTAs aside only costs)
+  static const int reducers = [] {
+    const char* e = getenv("B2_TWOSHOT_REDUCERS");
+    return e != nullptr ? std::max(0, atoi(e)) : 0;
+  }();
+  return reducers;
+}
+
 // Picks the K split S of the cluster kernel for `tiles` output tiles of `kblocks` K blocks: the largest S that
 // keeps every cluster resident in one wave and leaves each CTA at least two K blocks.  0 = use the stream-K kernel.
-template <int BN, int EPI>
-int pick_cluster_split(int tiles, int kblocks, int num_sms) {
-  if (!cluster_path_enabled() || tiles > num_sms) return 0;
+// resident(bn, S) = how many clusters of S CTAs fit on the device at once.
+template <class Resident>
+int pick_cluster_split(int bn, int tiles, int kblocks, int num_sms, Resident&& resident) {
+  if (tiles > num_sms) return 0;
   for (int S = 8; S >= 1; --S) {
     if (S > 1 && kblocks < 2 * S) continue;
     if (tiles * S > num_sms) continue;
-    if (max_resident_clusters<BN, EPI>(S) >= tiles) return S;
+    if (resident(bn, S) >= tiles) return S;
   }
   return 0;
+}
+
+// Pure host arithmetic: no CUDA call besides what `resident` makes.
+template <class Resident>
+int plan_gemm(int epi, int M, int N, int K, int num_sms, int min_grid, int reducers, int64_t tile_cap, bool clusters_on,
+              Resident&& resident, GemmPlan& p) {
+  if (M <= 0 || N <= 0 || K <= 0 || num_sms <= 0) return B2_ERR_ARG;
+  p.swap = (epi != EPI_PUSH2) && M <= 256;
+  if (p.swap) p.bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  else p.bn = (N >= 256) ? 256 : (N > 64 ? 128 : 64);
+  const int rowsP = p.swap ? N : M, rowsQ = p.swap ? M : N;
+  p.tilesP = (rowsP + BM - 1) / BM;
+  p.tilesQ = (rowsQ + p.bn - 1) / p.bn;
+  p.kblocks = (K + BK - 1) / BK;
+  const int64_t tiles = static_cast<int64_t>(p.tilesP) * p.tilesQ;
+  if (tiles > tile_cap) return B2_ERR_SHAPE;
+  const int64_t U = tiles * p.kblocks;
+  if (U > (1ll << 30)) return B2_ERR_SHAPE;
+  // every CTA should stream at least ~8 K blocks, or splitting costs more than it saves
+  int64_t g = std::max<int64_t>(1, U / 8);
+  const int sms_for_gemm = epi == EPI_PUSH2 ? std::max(1, num_sms - reducers) : num_sms;
+  g = std::min<int64_t>(g, sms_for_gemm);
+  g = std::min<int64_t>(g, U);
+  p.gemm_ctas = static_cast<int>(g);
+  p.round_robin = (!p.swap && tiles >= 4 * g) ? 1 : 0;
+  p.grid = (epi == EPI_PUSH2) ? num_sms : std::max(p.gemm_ctas, std::min(min_grid, num_sms));
+  p.cluster_split = 0;
+  if (epi != EPI_PUSH2 && clusters_on && p.swap && p.tilesQ == 1 && p.bn <= 64) {  // up to 64 tokens: the decode sizes
+    p.cluster_split = pick_cluster_split(p.bn, p.tilesP, p.kblocks, num_sms, resident);
+    if (p.cluster_split > 0) {
+      p.gemm_ctas = p.tilesP * p.cluster_split;
+      p.grid = p.gemm_ctas;
+    }
+  }
+  return B2_OK;
 }
 
 template <int EPI>
 int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K, GemmArgs& args,
                 int min_grid, cudaStream_t stream) {
-  const bool swap = (EPI != EPI_PUSH2) && M <= 256;
-  int bn;
-  if (swap) bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-  else bn = (N >= 256) ? 256 : (N > 64 ? 128 : 64);
+  const int reducers = EPI == EPI_PUSH2 ? twoshot_reducers() : 0;
+  GemmPlan plan;
+  const int prc = plan_gemm(EPI, M, N, K, ctx->num_sms, min_grid, reducers, ctx->tile_counter_cap, cluster_path_enabled(),
+                            [](int bn, int S) {
+                              if constexpr (EPI == EPI_PUSH2) return 0;
+                              else return bn == 32 ? max_resident_clusters<32, EPI>(S) : max_resident_clusters<64, EPI>(S);
+                            },
+                            plan);
+  if (prc != B2_OK) return prc;
+  const bool swap = plan.swap != 0;
+  const int bn = plan.bn;
   const int rowsP = swap ? N : M, rowsQ = swap ? M : N;
-  args.tilesP = (rowsP + BM - 1) / BM;
-  args.tilesQ = (rowsQ + bn - 1) / bn;
-  args.kblocks = (K + BK - 1) / BK;
+  args.tilesP = plan.tilesP;
+  args.tilesQ = plan.tilesQ;
+  args.kblocks = plan.kblocks;
   args.M = M;
   args.N = N;
   args.ws = ctx->splitk_ws;
   args.counters = ctx->tile_counters;
   args.status = ctx->status_dev;
   args.trace = ctx->trace_on ? ctx->trace : nullptr;
-  const int64_t tiles = static_cast<int64_t>(args.tilesP) * args.tilesQ;
-  if (tiles > ctx->tile_counter_cap) return B2_ERR_SHAPE;
-  const int64_t U = tiles * args.kblocks;
-  if (U > (1ll << 30)) return B2_ERR_SHAPE;
-  // every CTA should stream at least ~8 K blocks, or splitting costs more than it saves
-  int64_t g = std::max<int64_t>(1, U / 8);
-  int sms_for_gemm = ctx->num_sms;
-  if (EPI == EPI_PUSH2) {
-    // B2_TWOSHOT_REDUCERS=n sets n CTAs aside that only reduce, following the GEMM's sweep over the rows, so
-    // that the second half of the NVLink traffic overlaps the tensor-core work.  Default 0: every CTA reduces
-    // after its GEMM work (SM time, not NVLink, bounds most shapes, and then setting CTAs aside only costs)
-    static const int reducers = [] {
-      const char* e = getenv("B2_TWOSHOT_REDUCERS");
-      return e != nullptr ? atoi(e) : 0;
-    }();
-    args.dedicated_reducers = reducers > 0 ? 1 : 0;
-    sms_for_gemm = std::max(1, ctx->num_sms - std::max(0, reducers));
-  }
-  g = std::min<int64_t>(g, sms_for_gemm);
-  g = std::min<int64_t>(g, U);
-  args.gemm_ctas = static_cast<int>(g);
-  args.round_robin = (!swap && tiles >= 4 * g) ? 1 : 0;
-
-  const int grid = (EPI == EPI_PUSH2) ? ctx->num_sms : std::max(args.gemm_ctas, std::min(min_grid, ctx->num_sms));
+  args.dedicated_reducers = reducers > 0 ? 1 : 0;
+  args.gemm_ctas = plan.gemm_ctas;
+  args.round_robin = plan.round_robin;
+  const int grid = plan.grid;
 
   CUtensorMap tmP, tmQ;
   const void* pP = swap ? W : A;
@@ -1280,15 +1333,10 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
 
   g_last_gemm_path = 0;
   if constexpr (EPI != EPI_PUSH2) {
-    if (swap && args.tilesQ == 1 && bn <= 64) {  // up to 64 tokens: the decode sizes
-      const int S = bn == 32 ? pick_cluster_split<32, EPI>(args.tilesP, args.kblocks, ctx->num_sms)
-                             : pick_cluster_split<64, EPI>(args.tilesP, args.kblocks, ctx->num_sms);
-      if (S > 0) {
-        g_last_gemm_path = 1;
-        args.gemm_ctas = args.tilesP * S;
-        if (bn == 32) return launch_cluster_inst<32, EPI>(tmP, tmQ, args, args.tilesP, S, stream);
-        return launch_cluster_inst<64, EPI>(tmP, tmQ, args, args.tilesP, S, stream);
-      }
+    if (plan.cluster_split > 0) {
+      g_last_gemm_path = 1;
+      if (bn == 32) return launch_cluster_inst<32, EPI>(tmP, tmQ, args, args.tilesP, plan.cluster_split, stream);
+      return launch_cluster_inst<64, EPI>(tmP, tmQ, args, args.tilesP, plan.cluster_split, stream);
     }
     if (swap) {
       switch (bn) {
@@ -1646,4 +1694,88 @@ extern "C" int b2_gemm_static_scratch(const void* A, int64_t lda, const void* W,
   if (rc != B2_OK) return rc;
   if (bn == 32) return launch_inst<32, true, EPI_STORE>(tmP, tmQ, args, args.gemm_ctas, s);
   return launch_inst<64, true, EPI_STORE>(tmP, tmQ, args, args.gemm_ctas, s);
+}
+
+// ---------------------------------------------------------------------------
+// The planner as data, for tests that run without a GPU (no CUDA call here).
+// ---------------------------------------------------------------------------
+static_assert(sizeof(b2_gemm_plan) == sizeof(GemmPlan), "b2_gemm_plan mirrors GemmPlan");
+
+extern "C" int b2_plan_gemm(int epilogue, int M, int N, int K, int num_sms, const int* resident_clusters, b2_gemm_plan* plan) {
+  if (plan == nullptr || epilogue < EPI_STORE || epilogue > EPI_PUSH2) return B2_ERR_ARG;
+  GemmPlan p{};
+  const int min_grid = epilogue == EPI_PUSH ? M : 0;  // the one-shot launch also wants a CTA per token row for its reduce phase
+  const int rc = plan_gemm(epilogue, M, N, K, num_sms, min_grid, 0, 1 << 20, resident_clusters != nullptr,
+                           [&](int bn, int S) { return resident_clusters[(bn == 32 ? 0 : 9) + S]; }, p);
+  if (rc != B2_OK) return rc;
+  plan->swap = p.swap;
+  plan->bn = p.bn;
+  plan->tiles_p = p.tilesP;
+  plan->tiles_q = p.tilesQ;
+  plan->kblocks = p.kblocks;
+  plan->gemm_ctas = p.gemm_ctas;
+  plan->round_robin = p.round_robin;
+  plan->grid = p.grid;
+  plan->cluster_split = p.cluster_split;
+  return B2_OK;
+}
+
+extern "C" int b2_plan_cta_units(const b2_gemm_plan* plan, int cta, int* units, int cap) {
+  if (plan == nullptr || cta < 0 || cap < 0 || (cap > 0 && units == nullptr)) return -B2_ERR_ARG;
+  if (plan->cluster_split > 0) {  // gemm_cluster_kernel: tile = cluster index, K blocks split evenly over the cluster
+    const int S = plan->cluster_split, tile = cta / S, crank = cta % S;
+    if (tile >= plan->tiles_p) return 0;
+    const int base = plan->kblocks / S, rem = plan->kblocks % S;
+    const int kb0 = crank * base + (crank < rem ? crank : rem);
+    const int n = base + (crank < rem ? 1 : 0);
+    for (int i = 0; i < n && i < cap; ++i) {
+      units[3 * i] = tile;
+      units[3 * i + 1] = kb0 + i;
+      units[3 * i + 2] = i == 0 ? 1 : 0;
+    }
+    return n;
+  }
+  const int tiles = plan->tiles_p * plan->tiles_q;
+  const Work w = make_work(cta, plan->gemm_ctas, tiles, plan->kblocks, plan->round_robin != 0);
+  // the producer's walk (Cursor) and the consumers' walk (next_seg) must name the same units in the same order
+  Cursor c = cursor_begin(w, plan->tiles_q);
+  int i = 0, n = 0;
+  Seg s;
+  while (next_seg(w, i, s)) {
+    for (int kb = s.kb0; kb < s.kb1; ++kb, ++n) {
+      if (c.tile != s.tile || c.kb != kb || c.tp != s.tile / plan->tiles_q || c.tq != s.tile % plan->tiles_q) return -B2_ERR_SHAPE;
+      if (n < cap) {
+        units[3 * n] = s.tile;
+        units[3 * n + 1] = kb;
+        units[3 * n + 2] = kb == s.kb0 ? 1 : 0;
+      }
+      cursor_next(w, plan->tiles_q, c);
+    }
+  }
+  return n == w.n_units ? n : -B2_ERR_SHAPE;
+}
+
+extern "C" int b2_plan_tile_contributors(const b2_gemm_plan* plan, int tile, int* first_cta, int* last_cta) {
+  if (plan == nullptr || first_cta == nullptr || last_cta == nullptr || tile < 0 || tile >= plan->tiles_p * plan->tiles_q) return B2_ERR_ARG;
+  if (plan->cluster_split > 0) {
+    *first_cta = tile * plan->cluster_split;
+    *last_cta = *first_cta + plan->cluster_split - 1;
+  } else if (plan->round_robin) {
+    *first_cta = *last_cta = tile % plan->gemm_ctas;
+  } else {
+    const Work w = make_work(0, plan->gemm_ctas, plan->tiles_p * plan->tiles_q, plan->kblocks, false);
+    *first_cta = w.part.cta_of(tile * plan->kblocks);
+    *last_cta = w.part.cta_of(tile * plan->kblocks + plan->kblocks - 1);
+  }
+  return B2_OK;
+}
+
+extern "C" int b2_row_owner(int token, int world, int* local_row) {
+  if (token < 0 || world < 1 || local_row == nullptr) return -B2_ERR_ARG;
+  return owner_of(token, world, *local_row);
+}
+
+extern "C" int b2_owned_rows(int M, int world, int rank) {
+  if (M < 0 || world < 1 || rank < 0 || rank >= world) return -B2_ERR_ARG;
+  return owned_rows(M, world, rank);
 }

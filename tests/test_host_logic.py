@@ -1,9 +1,11 @@
-"""Host-side logic that needs no GPU: the stream-K work partition (a Python
-model of the arithmetic in csrc/b2_gemm.cu), and the layer classes' weight
-sharding at world size 1 and, under gloo, 2."""
+"""Host-side logic that needs no GPU: the GEMM launch planner and the two-shot row
+ownership (the library's own arithmetic, read through its b2_plan_* entry
+points), and the layer classes' weight sharding at world size 1 and, under gloo, 2."""
+import ctypes as C
 import os
 
 import pytest
+from hypothesis import given, settings, strategies as st
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -13,62 +15,145 @@ from oracle import tp_path as O
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-# ---- stream-K partition ------------------------------------------------------
-class Partition:
-    def __init__(self, units, ctas):
-        self.base, self.rem = divmod(units, ctas)
-
-    def u0(self, c):
-        return c * self.base + min(c, self.rem)
-
-    def cta_of(self, u):
-        big = self.rem * (self.base + 1)
-        return u // (self.base + 1) if u < big else self.rem + (u - big) // self.base
+# ---- the GEMM launch planner (the library's own arithmetic, read through b2_plan_gemm) ----
+EPI_STORE, EPI_PUSH, EPI_PUSH2 = 0, 1, 2
+SMS = 148
+# clusters of S CTAs resident at once, per tile width: [S] for 32-token tiles, [9 + S] for 64-token tiles.  On a GPU
+# the library asks the occupancy calculator; these stand for a 148-SM part whose clusters of 3, 5, 6 and 7 pack badly
+RESIDENT = [0, 148, 74, 44, 37, 26, 22, 18, 18] + [0, 148, 74, 44, 37, 26, 22, 18, 18]
 
 
-def gemm_ctas(units, sms=148):
-    return max(1, min(sms, units, max(1, units // 8)))
+def plan_gemm(abi, epi, m, n, k, sms=SMS, resident=RESIDENT):
+    plan = abi.GemmPlan()
+    res = (C.c_int * 18)(*resident) if resident is not None else None
+    rc = abi.lib.b2_plan_gemm(epi, m, n, k, sms, res, C.byref(plan))
+    return rc, plan
 
 
-def segments(p, c, kb):
-    u, end, out = p.u0(c), p.u0(c + 1), []
-    while u < end:
-        tile, k0 = divmod(u, kb)
-        ln = min(kb - k0, end - u)
-        out.append((tile, k0, k0 + ln))
-        u += ln
-    return out
+def cta_units(abi, plan, cta):
+    cap = 4096
+    buf = (C.c_int * (3 * cap))()
+    n = abi.lib.b2_plan_cta_units(C.byref(plan), cta, buf, cap)
+    assert n >= 0, f"producer and consumer walks disagree (code {-n})"
+    if n > cap:
+        cap = n
+        buf = (C.c_int * (3 * cap))()
+        assert abi.lib.b2_plan_cta_units(C.byref(plan), cta, buf, cap) == n
+    return [(buf[3 * i], buf[3 * i + 1], buf[3 * i + 2]) for i in range(n)]
 
 
-@pytest.mark.parametrize("tiles,kb", [(1, 1), (32, 64), (32, 192), (48, 64), (192, 64), (1187, 64), (1280, 16), (3, 5), (7, 400), (200, 3)])
-def test_streamk_partition_covers_every_unit_once(tiles, kb):
-    units = tiles * kb
-    g = gemm_ctas(units)
-    p = Partition(units, g)
-    assert p.u0(g) == units and p.base >= 1
-    seen = [0] * units
-    slots_used = {}
-    for c in range(g):
-        segs = segments(p, c, kb)
-        for u in range(p.u0(c), p.u0(c + 1)):
-            assert p.cta_of(u) == c
-        for i, (tile, k0, k1) in enumerate(segs):
-            for k in range(k0, k1):
-                seen[tile * kb + k] += 1
-        partial = [s for s in segs if not (s[1] == 0 and s[2] == kb)]
-        assert len(partial) <= 2
-    assert all(v == 1 for v in seen)
-    # contributors of a tile = CTAs from cta_of(first unit) to cta_of(last unit)
-    for tile in range(min(tiles, 64)):
-        first, last = p.cta_of(tile * kb), p.cta_of(tile * kb + kb - 1)
-        who = sorted({c for c in range(g) for (t, _, _) in segments(p, c, kb) if t == tile})
-        assert who == list(range(first, last + 1))
-    # a split tile accumulates in the slot of its first contributor: no two split tiles share one
-    owners = [p.cta_of(t * kb) for t in range(tiles) if p.cta_of(t * kb) != p.cta_of(t * kb + kb - 1)]
-    assert len(owners) == len(set(owners))
+def check_plan(abi, plan, m, n, k):
+    """Every K block of every output tile is computed exactly once, by the CTAs the combine step expects."""
+    tiles = plan.tiles_p * plan.tiles_q
+    rows_p, rows_q = (n, m) if plan.swap else (m, n)
+    assert plan.tiles_p * 128 >= rows_p > (plan.tiles_p - 1) * 128
+    assert plan.tiles_q * plan.bn >= rows_q > (plan.tiles_q - 1) * plan.bn
+    assert plan.kblocks * 64 >= k > (plan.kblocks - 1) * 64
+    assert 1 <= plan.gemm_ctas <= plan.grid <= SMS
+    seen = {}
+    holders = {}
+    for cta in range(plan.grid):
+        units = cta_units(abi, plan, cta)
+        if cta >= plan.gemm_ctas:
+            assert units == []
+        segs = 0
+        for i, (tile, kb, starts) in enumerate(units):
+            assert 0 <= tile < tiles and 0 <= kb < plan.kblocks
+            assert (tile, kb) not in seen, f"unit {(tile, kb)} computed by CTAs {seen[(tile, kb)]} and {cta}"
+            seen[(tile, kb)] = cta
+            holders.setdefault(tile, set()).add(cta)
+            if i > 0 and not starts:      # inside a segment: same tile, next K block (one accumulator, one commit)
+                assert (tile, kb) == (units[i - 1][0], units[i - 1][1] + 1)
+            else:
+                assert starts == 1
+            segs += starts
+        if plan.cluster_split == 0 and not plan.round_robin:
+            partial = sum(1 for t in {u[0] for u in units} if sum(1 for u in units if u[0] == t) < plan.kblocks)
+            assert partial <= 2           # a contiguous range cuts at most the tiles at its two ends
+    assert len(seen) == tiles * plan.kblocks
+    first, last = C.c_int(), C.c_int()
+    split_slots = []
+    for tile in range(tiles):
+        assert abi.lib.b2_plan_tile_contributors(C.byref(plan), tile, C.byref(first), C.byref(last)) == 0
+        assert sorted(holders[tile]) == list(range(first.value, last.value + 1)) or plan.round_robin
+        if plan.round_robin:
+            assert holders[tile] == {first.value} and first.value == last.value
+        if first.value != last.value and plan.cluster_split == 0:
+            split_slots.append(first.value)
+    # a split tile accumulates in the workspace slot of its first contributor: no two split tiles may share one
+    assert len(split_slots) == len(set(split_slots))
 
 
-# ---- weight loaders ------------------------------------------------------------
+PLAN_SHAPES = [
+    # (epilogue, M, N, K)                       what it is
+    (EPI_STORE, 64, 6144, 4096),                # qkv, Qwen3-8B decode, TP=1: cluster kernel
+    (EPI_STORE, 64, 24576, 4096),               # gate_up: 192 tiles > 148 SMs -> stream-K
+    (EPI_STORE, 64, 151936, 4096),              # LM head: 1187 tiles
+    (EPI_STORE, 1, 768, 4096), (EPI_STORE, 8, 4096, 512), (EPI_STORE, 33, 3072, 1024),
+    (EPI_STORE, 200, 1024, 4096), (EPI_STORE, 256, 12288, 4096),
+    (EPI_STORE, 257, 4096, 4096), (EPI_STORE, 4096, 4096, 4096), (EPI_STORE, 16384, 6144, 4096), (EPI_STORE, 1000, 40, 72),
+    (EPI_PUSH, 64, 4096, 4096), (EPI_PUSH, 64, 5120, 1024), (EPI_PUSH, 64, 5120, 3200), (EPI_PUSH, 256, 5120, 1024), (EPI_PUSH, 1, 1024, 384),
+    (EPI_PUSH2, 128, 5120, 1024), (EPI_PUSH2, 1024, 5120, 3200), (EPI_PUSH2, 8192, 5120, 1024), (EPI_PUSH2, 16384, 4096, 2048),
+    (EPI_PUSH2, 300, 1024, 1536),
+]
+
+
+@pytest.mark.parametrize("epi,m,n,k", PLAN_SHAPES)
+def test_planner_covers_every_unit_once(pkg, epi, m, n, k):
+    from nanovllm_b200 import _abi
+    rc, plan = plan_gemm(_abi, epi, m, n, k)
+    assert rc == 0
+    assert plan.swap == (1 if (epi != EPI_PUSH2 and m <= 256) else 0)
+    if epi == EPI_PUSH2:
+        assert plan.grid == SMS and plan.cluster_split == 0
+    check_plan(_abi, plan, m, n, k)
+
+
+def test_planner_choices_for_the_decode_shapes(pkg):
+    """The choices the measured numbers rest on: decode GEMMs of at most one wave of tiles go to the cluster kernel
+    with the largest K split that stays resident; 192 tiles go to stream-K on all SMs; prefill walks whole tiles."""
+    from nanovllm_b200 import _abi
+    rc, p = plan_gemm(_abi, EPI_STORE, 64, 6144, 4096)           # 48 tiles: 3 CTAs per tile would fit 148 SMs but
+    assert (p.bn, p.tiles_p, p.cluster_split) == (64, 48, 2)      # only 44 such clusters are resident -> split 2
+    assert p.grid == p.gemm_ctas == 96
+    rc, p = plan_gemm(_abi, EPI_STORE, 64, 4096, 4096)           # 32 tiles: split 4 (37 resident)
+    assert (p.tiles_p, p.cluster_split, p.grid) == (32, 4, 128)
+    rc, p = plan_gemm(_abi, EPI_STORE, 64, 24576, 4096)
+    assert (p.cluster_split, p.gemm_ctas, p.round_robin, p.bn) == (0, 148, 0, 64)
+    rc, p = plan_gemm(_abi, EPI_STORE, 64, 6144, 4096, resident=None)   # cluster kernel switched off
+    assert (p.cluster_split, p.gemm_ctas) == (0, 148)
+    rc, p = plan_gemm(_abi, EPI_STORE, 16384, 4096, 4096)
+    assert (p.swap, p.bn, p.round_robin, p.gemm_ctas) == (0, 256, 1, 148)
+    rc, p = plan_gemm(_abi, EPI_STORE, 16, 64, 64)                # one unit: one CTA
+    assert (p.gemm_ctas, p.grid) == (1, 1)
+    rc, p = plan_gemm(_abi, EPI_PUSH, 128, 64, 64)                # one-shot, stream-K kernel: one CTA has GEMM work, but
+    assert (p.cluster_split, p.gemm_ctas, p.grid) == (0, 1, 128)  # the launch keeps a CTA per token row for the reduce phase
+    rc, p = plan_gemm(_abi, EPI_PUSH, 64, 5120, 1024)             # one-shot at decode size: the cluster kernel reduces too
+    assert (p.tiles_p, p.cluster_split, p.grid) == (40, 3, 120)
+    for bad in [(0, 0, 64, 64), (0, 64, 0, 64), (0, 64, 64, 0), (3, 64, 64, 64)]:
+        assert plan_gemm(_abi, *bad)[0] == 1                      # B2_ERR_ARG
+    assert _abi.lib.b2_plan_gemm(0, 64, 64, 64, SMS, None, None) == 1
+
+
+@settings(max_examples=120, deadline=None)
+@given(epi=st.sampled_from([EPI_STORE, EPI_PUSH, EPI_PUSH2]), m=st.integers(1, 3000), n8=st.integers(1, 1200), k8=st.integers(1, 700),
+       sms=st.sampled_from([148, 132, 7, 1]))
+def test_planner_property(epi, m, n8, k8, sms):
+    import __graft_entry__
+    __graft_entry__.load_package()
+    from nanovllm_b200 import _abi
+    rc, plan = plan_gemm(_abi, epi, m, n8 * 8, k8 * 8, sms=sms, resident=[0, sms, sms // 2, sms // 3, sms // 4, sms // 5, sms // 6, sms // 7, sms // 8] * 2)
+    assert rc == 0
+    tiles = plan.tiles_p * plan.tiles_q
+    seen = set()
+    for cta in range(plan.grid):
+        for (tile, kb, _) in cta_units(_abi, plan, cta):
+            assert (tile, kb) not in seen
+            seen.add((tile, kb))
+    assert len(seen) == tiles * plan.kblocks
+    assert plan.gemm_ctas <= plan.grid <= max(sms, plan.gemm_ctas)
+
+
 def _golden(name):
     return torch.load(os.path.join(ROOT, "tests", "golden", name + ".pt"))
 
@@ -137,41 +222,34 @@ def test_layers_fail_loudly_without_cuda(pkg):
         TPRuntime(0, 1, 0, 16, 64)
 
 
-# ---- two-shot ownership of token rows (owner_of / owned_rows in csrc/b2_gemm.cu) ----
-def owner_of(token, world):
-    b = token >> 4
-    return b % world, ((b // world) << 4) + (token & 15)
-
-
-def owned_rows(m, world, rank):
-    blocks = (m + 15) >> 4
-    mine = (blocks - rank + world - 1) // world
-    if mine <= 0:
-        return 0
-    last_block = rank + (mine - 1) * world
-    last_rows = m - (last_block << 4) if last_block == blocks - 1 else 16
-    return (mine - 1) * 16 + last_rows
-
-
+# ---- two-shot ownership of token rows (the library's own owner_of / owned_rows, through b2_row_owner / b2_owned_rows) ----
 @pytest.mark.parametrize("m", [1, 15, 16, 17, 128, 200, 300, 777, 1024, 4096, 16384])
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_two_shot_row_ownership(m, world):
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
+def test_two_shot_row_ownership(pkg, m, world):
+    from nanovllm_b200 import _abi
+    lib = _abi.lib
+
+    def owner_of(t):
+        local = C.c_int()
+        return lib.b2_row_owner(t, world, C.byref(local)), local.value
+
     per_rank = {r: [] for r in range(world)}
     for t in range(m):
-        o, l = owner_of(t, world)
+        o, l = owner_of(t)
         per_rank[o].append(l)
     for r in range(world):
-        n = owned_rows(m, world, r)
+        n = lib.b2_owned_rows(m, world, r)
         # the owner's local rows are exactly 0 .. n-1, each once: the reduce phase walks them as a dense range
         assert sorted(per_rank[r]) == list(range(n)), (m, world, r)
         # and the reduce phase's inverse map (local row -> token) lands on this rank's tokens
         for row in range(n):
             token = (((row >> 4) * world + r) << 4) + (row & 15)
-            assert token < m and owner_of(token, world) == (r, row)
-    assert sum(owned_rows(m, world, r) for r in range(world)) == m
+            assert token < m and owner_of(token) == (r, row)
+    assert sum(lib.b2_owned_rows(m, world, r) for r in range(world)) == m
     # the inbox is sized for the rank that owns most
     max_rows = ((16384 + 15) // 16 + world - 1) // world * 16
-    assert max(owned_rows(min(m, 16384), world, r) for r in range(world)) <= max_rows
+    assert max(lib.b2_owned_rows(min(m, 16384), world, r) for r in range(world)) <= max_rows
+    assert lib.b2_owned_rows(m, world, world) < 0 and lib.b2_row_owner(-1, world, C.byref(C.c_int())) < 0
 
 
 # ---- cluster kernel: 4-column groups of the accumulator dealt round-robin to the S CTAs of a cluster ----
