@@ -240,6 +240,37 @@ int b2_embed(b2_ctx* ctx, const int64_t* ids, const void* W, int64_t vocab_start
 int b2_lm_head(b2_ctx* ctx, const void* h, int64_t ldh, const int32_t* row_index, const void* W, int64_t ldw,
                int B, int Vr, int H, void** logits_out, void* stream);
 
+/* ---- LM head fused with the sampler: replaces ParallelLMHead.forward
+ *      (nanovllm/layers/embed_head.py:56-66) followed by Sampler.forward
+ *      (nanovllm/layers/sampler.py:7-12), as run on rank 0 by
+ *      ModelRunner.run (nanovllm/engine/model_runner.py:212-218) -------------
+ * No [B, vocab] logits are stored or gathered.  The reference draws
+ *   token = argmax_i softmax(logits / T)_i / E_i,   E_i ~ Exp(1);
+ * since the softmax denominator is common to a row, that is
+ *   token = argmax_i (bf16(logit_i) / T - log E_i),
+ * which every rank evaluates over its own vocabulary slice inside the GEMM
+ * epilogue; only the best (score, vocab id) per row travels to rank 0.
+ * temperatures: fp32 [B] on the device, or NULL for greedy decoding
+ * (token = argmax_i logit_i, lowest id on ties: the reference at T -> 0).
+ * E_i = -log(u), u from Philox4x32-10 keyed by `seed` with counter (vocab id,
+ * row / 4, number of b2_lm_head_sample calls so far on this context, tag):
+ * independent of the tensor-parallel split, different on every call (also on
+ * every replay of a captured CUDA graph), reproducible from the seed.  It is
+ * the reference's distribution, not its random stream (torch's generator).
+ * tokens_out: int64 [B], written on rank 0 only (the reference samples on
+ * rank 0).  B <= 256 (B2_ERR_SHAPE otherwise: use b2_lm_head).  row_index as
+ * in b2_lm_head.  Counts as one collective call in every rank's sequence;
+ * two calls must be separated by an exchange that rank 0 completes after
+ * reading the first one's result (b2_broadcast_tokens does). */
+int b2_lm_head_sample(b2_ctx* ctx, const void* h, int64_t ldh, const int32_t* row_index, const void* W, int64_t ldw,
+                      int B, int Vr, int H, const float* temperatures, uint64_t seed, int64_t* tokens_out, void* stream);
+
+/* Host copies of the fused sampler's generator, for tests (no CUDA call): the
+ * 32 random bits behind E for (vocab_id, row `token`) in call number `call`
+ * (u = ((bits >> 9) + 0.5) * 2^-23), and Philox4x32-10 itself. */
+int b2_sampler_noise_bits(uint64_t seed, uint32_t vocab_id, uint32_t token, uint32_t call, uint32_t* bits);
+int b2_philox4x32_10(const uint32_t counter[4], const uint32_t key[2], uint32_t out[4]);
+
 /* ---- sampled-token broadcast: replaces the data the reference ships from
  *      rank 0 to the other ranks inside its pickled "run" message
  *      (nanovllm/engine/model_runner.py:76-89: the next step's last_token of
@@ -301,7 +332,7 @@ typedef struct b2_gemm_plan {
 } b2_gemm_plan;
 
 /* epilogue: 0 = b2_gemm / b2_lm_head / b2_gemm_silu_mul / b2_qkv_fused,
- * 1 = b2_rowpar_fused, 2 = b2_rowpar_fused_twoshot.  resident_clusters: NULL
+ * 1 = b2_rowpar_fused, 2 = b2_rowpar_fused_twoshot, 3 = b2_lm_head_sample.  resident_clusters: NULL
  * (cluster kernel not considered) or int[18]: entry [S] for 32-token tiles and
  * [9 + S] for 64-token tiles = clusters of S CTAs the device holds at once
  * (on a GPU the library asks the occupancy calculator). */

@@ -63,6 +63,9 @@ SIGNATURES = {
     "b2_store_kvcache": [_p, _i64, _p, _i64, _p, _p, _p, _i, _i, _p],
     "b2_embed": [_p, _p, _p, _i64, _i64, _i, _i, _p, _p],
     "b2_lm_head": [_p, _p, _i64, _p, _p, _i64, _i, _i, _i, C.POINTER(_p), _p],
+    "b2_lm_head_sample": [_p, _p, _i64, _p, _p, _i64, _i, _i, _i, _p, C.c_uint64, _p, _p],
+    "b2_sampler_noise_bits": [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32)],
+    "b2_philox4x32_10": [C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)],
     "b2_silu_and_mul": [_p, _i64, _i, _i, _p, _p],
     "b2_qk_norm_rope_store": [_p, _i64, _i, _i, _i, _i, _p, _p, _f, _p, _p, _p, _p, _p, _p],
     "b2_argmax": [_p, _i64, _i, _i, _p, _p],

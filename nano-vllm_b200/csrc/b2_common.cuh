@@ -39,7 +39,7 @@ struct B2DeviceState {
   unsigned int lmhead_seq;
   unsigned int lmhead_done;
   unsigned int bcast_seq;
-  unsigned int pad;
+  unsigned int sample_seq;     // fused LM-head sampler calls so far (part of the noise counter, so graph replays draw afresh)
 };
 
 // Host-visible (mapped, pinned) status word.
@@ -308,6 +308,7 @@ struct b2_ctx {
   size_t off_flags;     // [world] uint32 arrival flags for the logits gather
   size_t off_out;       // two-shot: [max_tokens][hidden] bf16 normed rows, written by their owner ranks
   size_t off_rowcnt;    // two-shot: [2 parity] uint32 rows received in off_out
+  size_t off_keybox;    // fused sampler, used on rank 0: [2 parity][world][max_seqs] uint64 best (score, vocab id) of every rank
   size_t off_tokens;    // [2 parity][max_seqs] int64 token inbox, -1 = not written
 
   // rank-local scratch
@@ -319,6 +320,7 @@ struct b2_ctx {
   B2Status* status_host;  // mapped pinned host memory
   B2Status* status_dev;   // device alias of status_host
   __nv_bfloat16* gather_rows;  // [max_seqs][hidden] staging for the LM head
+  unsigned long long* sample_keys;  // [max_seqs] fused sampler: this rank's best key per row, zero between calls
   unsigned long long* trace;   // [num_sms][8][2] phase stamps of the last GEMM launch
   bool trace_on;
 };

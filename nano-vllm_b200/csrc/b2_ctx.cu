@@ -135,6 +135,8 @@ static int ctx_init(b2_ctx* c) {
   if (W > 1) off = align_up(off + static_cast<size_t>(c->cfg.max_tokens) * H * 2, 1024);
   c->off_rowcnt = off;
   off = align_up(off + 64, 1024);
+  c->off_keybox = off;
+  off = align_up(off + 2 * W * static_cast<size_t>(c->cfg.max_seqs > 0 ? c->cfg.max_seqs : 1) * 8, 1024);
   c->off_tokens = off;
   off = align_up(off + 2 * static_cast<size_t>(c->cfg.max_seqs > 0 ? c->cfg.max_seqs : 1) * 8, 1024);
   c->symm_bytes = off;
@@ -166,6 +168,10 @@ static int ctx_init(b2_ctx* c) {
   c->status_host->rank = c->cfg.rank;
   B2_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&c->status_dev), c->status_host, 0));
   if (c->cfg.max_seqs > 0) B2_CUDA(cudaMalloc(&c->gather_rows, static_cast<size_t>(c->cfg.max_seqs) * H * 2));
+  if (c->cfg.max_seqs > 0) {
+    B2_CUDA(cudaMalloc(&c->sample_keys, static_cast<size_t>(c->cfg.max_seqs) * 8));
+    B2_CUDA(cudaMemset(c->sample_keys, 0, static_cast<size_t>(c->cfg.max_seqs) * 8));
+  }
   B2_CUDA(cudaMalloc(&c->trace, static_cast<size_t>(c->num_sms) * 16 * sizeof(unsigned long long)));
   B2_CUDA(cudaMemset(c->trace, 0, static_cast<size_t>(c->num_sms) * 16 * sizeof(unsigned long long)));
   c->trace_on = false;
@@ -209,6 +215,7 @@ int b2_ctx_destroy(b2_ctx* c) {
   cudaFree(c->dstate);
   cudaFree(c->trace);
   if (c->gather_rows) cudaFree(c->gather_rows);
+  if (c->sample_keys) cudaFree(c->sample_keys);
   if (c->status_host) cudaFreeHost(c->status_host);
   cudaGetLastError();  // a failed free of a never-made allocation is not an error of the caller
   delete c;

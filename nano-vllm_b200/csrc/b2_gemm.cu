@@ -42,6 +42,12 @@
 //              arrival counter.  A launch ends when its rank has received all rows
 //              it does not own.  NVLink carries 2 (tp-1)/tp M N 2 bytes per rank,
 //              the minimum for an all-reduce.
+//   EPI_SAMPLE the LM head fused with the sampler: no logits are stored.  Every
+//              (token, vocab entry) score - the bf16-rounded logit, divided by the
+//              row's temperature plus Gumbel noise from a counter-based generator,
+//              or the logit alone for greedy decoding - is packed with its vocab id
+//              into a 64-bit key whose unsigned order is (score, lowest id first);
+//              the kernel keeps the largest key per token row.
 //
 // Every kernel is launched with the programmatic-dependent-launch attribute:
 // set-up and the first ring of weight tiles are issued before
@@ -61,7 +67,8 @@ constexpr int NUM_THREADS = 192;
 constexpr int MAX_ROW_VECS = 6;  // 16-byte vectors of one row per thread in the reduce phase
 constexpr uint64_t PIPE_LIMIT_NS = 1000000000ull;  // no wait inside the GEMM pipeline lasts anywhere near this
 
-enum { EPI_STORE = 0, EPI_PUSH = 1, EPI_PUSH2 = 2 };
+enum { EPI_STORE = 0, EPI_PUSH = 1, EPI_PUSH2 = 2, EPI_SAMPLE = 3 };
+__host__ __device__ constexpr bool is_push(int epi) { return epi == EPI_PUSH || epi == EPI_PUSH2; }  // epilogues of the fused row-parallel call
 
 struct GemmArgs {
   int tilesP, tilesQ, kblocks;
@@ -103,6 +110,11 @@ struct GemmArgs {
   size_t out_off, rowcnt_off;  // from inbox[r]: that rank's [max_tokens][hidden] output buffer and its [2] rows-received counters
   int rows_per_rank;
   unsigned long long* trace;  // optional [CTA][8][2] (SM clock, global ns) phase stamps; null = off
+  // EPI_SAMPLE (LM head fused with the sampler; feature-lane layout only, features = vocabulary entries)
+  unsigned long long* sample_keys;  // [M] best (score, vocab id) per token row, zero between calls
+  const float* temperatures;        // [M], or null = greedy
+  unsigned long long seed;
+  int vocab_offset;                 // vocabulary id of feature 0 (rank * vocab / world)
 };
 
 template <int BN>
@@ -363,15 +375,89 @@ __device__ __forceinline__ void flush_rows(const GemmArgs& a, unsigned char* wbu
   __syncwarp();
 }
 
+// ---------------------------------------------------------------------------
+// Sampler fused into the LM-head epilogue.
+// The reference draws token = argmax_i softmax(logit / T)_i / E_i with E_i ~ Exp(1)
+// (nanovllm/layers/sampler.py:9-11).  The softmax denominator is the same for every i of a row and log is
+// monotone, so the same token is argmax_i (logit_i / T - log E_i): no pass over the whole row is needed,
+// each rank can scan its own slice of the vocabulary, and only (best score, vocab id) per row is exchanged.
+// E_i comes from Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11) keyed by
+// the caller's seed, with counter (vocab id, token row / 4, call number, tag): the draw for an element depends
+// on nothing but those, so it is the same for every tensor-parallel split and can be regenerated on the host.
+// ---------------------------------------------------------------------------
+constexpr uint32_t SAMPLE_TAG = 0x53414D50u;
+
+__host__ __device__ __forceinline__ void philox4x32_10(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const uint64_t p0 = static_cast<uint64_t>(0xD2511F53u) * c[0], p1 = static_cast<uint64_t>(0xCD9E8D57u) * c[2];
+    const uint32_t n0 = static_cast<uint32_t>(p1 >> 32) ^ c[1] ^ k0, n2 = static_cast<uint32_t>(p0 >> 32) ^ c[3] ^ k1;
+    c[1] = static_cast<uint32_t>(p1);
+    c[3] = static_cast<uint32_t>(p0);
+    c[0] = n0;
+    c[2] = n2;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+}
+// 23 random bits -> u in (0, 1), both ends excluded and every value exact in fp32; E = -log u is Exp(1)
+__device__ __forceinline__ float gumbel_from_bits(uint32_t x) {
+  const float u = (static_cast<float>(x >> 9) + 0.5f) * 1.1920928955078125e-07f;  // 2^-23
+  return -logf(-logf(u));
+}
+// unsigned order of the key = (score ascending, then vocab id descending): max picks the best score, lowest id on ties
+__host__ __device__ __forceinline__ unsigned long long sample_key(uint32_t score_bits, uint32_t vocab_id) {
+  const uint32_t ord = (score_bits & 0x80000000u) ? ~score_bits : (score_bits | 0x80000000u);
+  return (static_cast<unsigned long long>(ord) << 32) | (0xFFFFFFFFu - vocab_id);
+}
+
+// One 32-token chunk of one vocabulary entry per lane (feature-lane layout).  The 32 x 32 keys of the warp are
+// reduced over the lanes by a halving exchange (31 shuffles of a key instead of 32 x 5): afterwards lane l holds
+// the best key of token token0 + l among the warp's 32 vocabulary entries, and merges it into the CTA's table.
+__device__ __forceinline__ void sample_feature_lanes(const GemmArgs& a, float (&v)[32], int feature, int token0, int lane,
+                                                     unsigned int call, unsigned long long* cta_best) {
+  const bool live = feature < a.N;
+  const uint32_t vocab_id = static_cast<uint32_t>(a.vocab_offset + feature);
+  const float bias = (a.bias != nullptr && live) ? __uint_as_float(static_cast<uint32_t>(a.bias[feature]) << 16) : 0.f;
+  unsigned long long k[32];
+#pragma unroll
+  for (int j0 = 0; j0 < 32; j0 += 4) {
+    uint32_t r[4] = {vocab_id, static_cast<uint32_t>(token0 + j0) >> 2, call, SAMPLE_TAG};
+    if (a.temperatures != nullptr) philox4x32_10(r, static_cast<uint32_t>(a.seed), static_cast<uint32_t>(a.seed >> 32));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int token = token0 + j0 + i;
+      float z = b2::bf16_round(v[j0 + i] + bias);  // the logit as the unfused path stores it
+      if (a.temperatures != nullptr && token < a.M) z = z / __ldg(a.temperatures + token) + gumbel_from_bits(r[i]);
+      k[j0 + i] = (live && token < a.M) ? sample_key(__float_as_uint(z), vocab_id) : 0ull;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) {
+    const bool upper = (lane & o) != 0;
+#pragma unroll
+    for (int j = 0; j < o; ++j) {
+      const unsigned long long send = upper ? k[j] : k[j + o];
+      const unsigned long long keep = upper ? k[j + o] : k[j];
+      const unsigned long long recv = __shfl_xor_sync(0xffffffffu, send, o);
+      k[j] = keep > recv ? keep : recv;
+    }
+  }
+  if (k[0] != 0ull) atomicMax(cta_best + token0 + lane, k[0]);
+}
+
 // One 32-column chunk c of a tile leaves the registers.  Feature-lane layout (SWAP): stored at once.
 // Token-row layout: parked in the warp's staging buffer; every fourth chunk (and the tile's last) flushes.
 template <int BN, bool SWAP, int EPI>
 __device__ __forceinline__ void emit_chunk(const GemmArgs& a, float (&v)[32], int p_row, int q_tile0, int c, int lane, unsigned int parity,
-                                           unsigned char* wbuf) {
-  if (SWAP) {
+                                           unsigned char* wbuf, unsigned int sample_call, unsigned long long* cta_best) {
+  if constexpr (EPI == EPI_SAMPLE) {
+    static_assert(SWAP, "the fused sampler needs the feature-lane layout");
+    sample_feature_lanes(a, v, p_row, q_tile0 + c * 32, lane, sample_call, cta_best);
+  } else if (SWAP) {
     emit_feature_lanes<32, EPI>(a, v, p_row, q_tile0 + c * 32, lane, parity);
   } else {
-    stage_row_chunk(a, wbuf, lane, c & 3, v, q_tile0 + c * 32, EPI != EPI_STORE);
+    stage_row_chunk(a, wbuf, lane, c & 3, v, q_tile0 + c * 32, is_push(EPI));
     if ((c & 3) == 3 || c == BN / 32 - 1)
       flush_rows<EPI>(a, wbuf, lane, p_row - lane, q_tile0 + (c & ~3) * 32, ((c & 3) + 1) * 4, parity);
   }
@@ -549,7 +635,7 @@ __device__ __forceinline__ void stamp(const GemmArgs& a, int slot) {
 template <int EPI>
 __device__ __forceinline__ void fused_tail(const GemmArgs& a, unsigned int parity, float* red, volatile int* abort_flag, int aborted) {
   if (threadIdx.x == 0) stamp(a, 5);
-  if (EPI != EPI_STORE) {
+  if (is_push(EPI)) {
     if (!aborted) {
       if (EPI == EPI_PUSH) {
         switch (a.world) {
@@ -607,6 +693,19 @@ __device__ __forceinline__ void fused_tail(const GemmArgs& a, unsigned int parit
   }
 }
 
+// The CTA's table of best keys per token row (fused sampler only; other epilogues carry no such array)
+template <int EPI>
+struct SampleTable {
+  __device__ static __forceinline__ unsigned long long* get() { return nullptr; }
+};
+template <>
+struct SampleTable<EPI_SAMPLE> {
+  __device__ static __forceinline__ unsigned long long* get() {
+    __shared__ unsigned long long table[256];
+    return table;
+  }
+};
+
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
@@ -628,6 +727,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * ACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   __shared__ float red[NUM_THREADS / 32];
+  unsigned long long* const cta_best = SampleTable<EPI>::get();
+  unsigned int sample_call = 0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x;
@@ -651,6 +752,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
     *abort_flag = 0;
     b2::mbar_fence_init();
   }
+  if constexpr (EPI == EPI_SAMPLE)
+    for (int t = threadIdx.x; t < 256; t += NUM_THREADS) cta_best[t] = 0ull;
   if (warp == 1 && has_gemm) {
     b2::tmem_alloc(b2::smem_u32(tmem_slot), C::TMEM_COLS);
     b2::tmem_relinquish();
@@ -747,7 +850,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
       const int q = warp & 3;  // TMEM lane quadrant this warp may read
       unsigned char* wbuf = smem + STAGES * C::STAGE_BYTES + 256 + q * STAGING_BYTES_PER_WARP;  // token-row layout only
       b2::pdl_wait();
-      if (EPI != EPI_STORE) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
+      if (is_push(EPI)) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
+      if constexpr (EPI == EPI_SAMPLE) sample_call = *reinterpret_cast<volatile unsigned int*>(&a.dstate->sample_seq);
       int u = 0, seg = 0;
       Seg s;
       while (next_seg(work, u, s)) {
@@ -768,7 +872,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-            emit_chunk<BN, SWAP, EPI>(a, v, p_row, tq * BN, c, lane, parity, wbuf);
+            emit_chunk<BN, SWAP, EPI>(a, v, p_row, tq * BN, c, lane, parity, wbuf, sample_call, cta_best);
           }
         } else {
           // This CTA holds only part of the tile's K range.  Every contributor adds its part into the
@@ -808,7 +912,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
               }
 #pragma unroll
               for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(slot + (c * 8 + j) * 128) = make_float4(0.f, 0.f, 0.f, 0.f);
-              emit_chunk<BN, SWAP, EPI>(a, v, p_row, tq * BN, c, lane, parity, wbuf);
+              emit_chunk<BN, SWAP, EPI>(a, v, p_row, tq * BN, c, lane, parity, wbuf, sample_call, cta_best);
             }
           }
         }
@@ -823,7 +927,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
 
   // ---- all roles meet; tensor memory goes back ------------------------------
   b2::pdl_wait();
-  if (EPI != EPI_STORE) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
+  if (is_push(EPI)) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
   __syncwarp();
   b2::tc_fence_before();
   __syncthreads();
@@ -835,6 +939,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
     if (threadIdx.x == 0) b2::report_timeout(a.status, aborted);
   }
   if (warp == 1 && has_gemm) b2::tmem_dealloc(tmem_base, C::TMEM_COLS);
+  if constexpr (EPI == EPI_SAMPLE) {
+    // the CTA's best key per token row joins the launch-wide table (feature-lane layout: one token tile, row = token)
+    for (int t = threadIdx.x; t < BN; t += NUM_THREADS)
+      if (t < a.M && cta_best[t] != 0ull) atomicMax(a.sample_keys + t, cta_best[t]);
+  }
 
   fused_tail<EPI>(a, parity, red, abort_flag, aborted);
 }
@@ -975,7 +1084,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
     const int q = warp & 3;
     const int f = q * 32 + lane;  // feature row of the tile this thread holds
     b2::pdl_wait();
-    if (EPI != EPI_STORE) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
+    if (is_push(EPI)) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
     if (EPI == EPI_STORE && a.qkv_fused) {
       const bool rotated = tile < a.nq + a.nkv;
 #pragma unroll
@@ -1137,7 +1246,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
 
   // ---- all roles meet; tensor memory goes back ------------------------------
   b2::pdl_wait();
-  if (EPI != EPI_STORE) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
+  if (is_push(EPI)) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
   __syncwarp();
   b2::tc_fence_before();
   __syncthreads();
@@ -1283,7 +1392,7 @@ int plan_gemm(int epi, int M, int N, int K, int num_sms, int min_grid, int reduc
   p.round_robin = (!p.swap && tiles >= 4 * g) ? 1 : 0;
   p.grid = (epi == EPI_PUSH2) ? num_sms : std::max(p.gemm_ctas, std::min(min_grid, num_sms));
   p.cluster_split = 0;
-  if (epi != EPI_PUSH2 && clusters_on && p.swap && p.tilesQ == 1 && p.bn <= 64) {  // up to 64 tokens: the decode sizes
+  if ((epi == EPI_STORE || epi == EPI_PUSH) && clusters_on && p.swap && p.tilesQ == 1 && p.bn <= 64) {  // up to 64 tokens: the decode sizes
     p.cluster_split = pick_cluster_split(p.bn, p.tilesP, p.kblocks, num_sms, resident);
     if (p.cluster_split > 0) {
       p.gemm_ctas = p.tilesP * p.cluster_split;
@@ -1300,7 +1409,7 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
   GemmPlan plan;
   const int prc = plan_gemm(EPI, M, N, K, ctx->num_sms, min_grid, reducers, ctx->tile_counter_cap, cluster_path_enabled(),
                             [](int bn, int S) {
-                              if constexpr (EPI == EPI_PUSH2) return 0;
+                              if constexpr (EPI == EPI_PUSH2 || EPI == EPI_SAMPLE) return 0;
                               else return bn == 32 ? max_resident_clusters<32, EPI>(S) : max_resident_clusters<64, EPI>(S);
                             },
                             plan);
@@ -1332,12 +1441,14 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
   if (rc != B2_OK) return rc;
 
   g_last_gemm_path = 0;
-  if constexpr (EPI != EPI_PUSH2) {
+  if constexpr (EPI == EPI_STORE || EPI == EPI_PUSH) {
     if (plan.cluster_split > 0) {
       g_last_gemm_path = 1;
       if (bn == 32) return launch_cluster_inst<32, EPI>(tmP, tmQ, args, args.tilesP, plan.cluster_split, stream);
       return launch_cluster_inst<64, EPI>(tmP, tmQ, args, args.tilesP, plan.cluster_split, stream);
     }
+  }
+  if constexpr (EPI != EPI_PUSH2) {
     if (swap) {
       switch (bn) {
         case 32: return launch_inst<32, true, EPI>(tmP, tmQ, args, grid, stream);
@@ -1347,10 +1458,14 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
       }
     }
   }
-  switch (bn) {
-    case 64: return launch_inst<64, false, EPI>(tmP, tmQ, args, grid, stream);
-    case 128: return launch_inst<128, false, EPI>(tmP, tmQ, args, grid, stream);
-    default: return launch_inst<256, false, EPI>(tmP, tmQ, args, grid, stream);
+  if constexpr (EPI == EPI_SAMPLE) {
+    return B2_ERR_SHAPE;  // the fused sampler exists in the feature-lane layout only (at most 256 token rows)
+  } else {
+    switch (bn) {
+      case 64: return launch_inst<64, false, EPI>(tmP, tmQ, args, grid, stream);
+      case 128: return launch_inst<128, false, EPI>(tmP, tmQ, args, grid, stream);
+      default: return launch_inst<256, false, EPI>(tmP, tmQ, args, grid, stream);
+    }
   }
 }
 
@@ -1407,6 +1522,63 @@ __global__ void lm_head_sync_kernel(int rank, int world, unsigned int* flags_ran
   dstate->lmhead_seq = want;
 }
 
+// Completion of the fused LM-head sampler.  One block.  Every rank hands its best key per row to rank 0
+// (its own slot of rank 0's key box, then the call number in rank 0's flag word); rank 0 waits for the
+// peers, keeps the largest key of each row and writes the vocabulary ids.  The local table goes back to
+// zero and the call counters advance.  The key box alternates between two halves by call number.
+__global__ void __launch_bounds__(256) sample_finish_kernel(int rank, int world, int B, int max_seqs, unsigned long long* keys,
+                                                            unsigned long long* keybox_rank0, unsigned int* flags_rank0,
+                                                            B2DeviceState* dstate, B2Status* status, uint64_t timeout_ns,
+                                                            int64_t* tokens_out) {
+  b2::pdl_wait();
+  const unsigned int want = dstate->lmhead_seq + 1;
+  unsigned long long* box = keybox_rank0 + static_cast<size_t>(want & 1u) * world * max_seqs;
+  const int t = threadIdx.x;
+  unsigned long long best = 0ull;
+  if (t < B) {
+    best = keys[t];
+    keys[t] = 0ull;
+  }
+  if (world > 1) {
+    if (rank != 0) {
+      if (t < B) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(box + static_cast<size_t>(rank) * max_seqs + t), "l"(best) : "memory");
+      __threadfence_system();
+      __syncthreads();
+      if (t == 0) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags_rank0 + rank), "r"(want) : "memory");
+    } else {
+      if (t == 0) {
+        const uint64_t t0 = b2::globaltimer_ns();
+        for (int r = 1; r < world; ++r) {
+          for (uint32_t spin = 0;; ++spin) {
+            unsigned int got;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(flags_rank0 + r) : "memory");
+            if (static_cast<int>(got - want) >= 0) break;
+            if ((spin & 0xFF) == 0xFF && b2::globaltimer_ns() - t0 > timeout_ns) {
+              b2::report_timeout(status, B2_WAIT_LOGITS);
+              break;
+            }
+          }
+        }
+        __threadfence_system();
+      }
+      __syncthreads();
+      if (t < B) {
+        for (int r = 1; r < world; ++r) {
+          unsigned long long k;
+          asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(k) : "l"(box + static_cast<size_t>(r) * max_seqs + t) : "memory");
+          best = k > best ? k : best;
+        }
+      }
+    }
+  }
+  if (rank == 0 && t < B) tokens_out[t] = static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(best));
+  __syncthreads();
+  if (t == 0) {
+    dstate->lmhead_seq = want;
+    dstate->sample_seq += 1;
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -1443,6 +1615,62 @@ int b2_lm_head(b2_ctx* ctx, const void* h, int64_t ldh, const int32_t* row_index
                       ctx->dstate, ctx->status_dev, static_cast<uint64_t>(ctx->cfg.timeout_ms) * 1000000ull));
   }
   if (rank == 0) *logits_out = ctx->symm + ctx->off_logits;
+  return B2_OK;
+}
+
+int b2_lm_head_sample(b2_ctx* ctx, const void* h, int64_t ldh, const int32_t* row_index, const void* W, int64_t ldw, int B, int Vr,
+                      int H, const float* temperatures, uint64_t seed, int64_t* tokens_out, void* stream) {
+  if (ctx == nullptr) return B2_ERR_ARG;
+  int rc = check_operands(h, ldh, W, ldw, B, Vr, H);
+  if (rc != B2_OK) return rc;
+  const int world = ctx->cfg.world, rank = ctx->cfg.rank;
+  if (rank == 0 && tokens_out == nullptr) return B2_ERR_ARG;
+  if (ctx->cfg.vocab <= 0 || ctx->cfg.max_seqs <= 0) return B2_ERR_STATE;
+  if (B > ctx->cfg.max_seqs || static_cast<int64_t>(Vr) * world != ctx->cfg.vocab || H > ctx->cfg.hidden) return B2_ERR_SHAPE;
+  if (B > 256) return b2::set_error(B2_ERR_SHAPE, "b2_lm_head_sample: %d rows; the fused sampler takes at most 256, use b2_lm_head", B);
+  if (!ctx->peers_ready) return B2_ERR_STATE;
+  if (B == 0) return B2_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const void* A = h;
+  int64_t lda = ldh;
+  if (row_index != nullptr) {
+    const int64_t work = static_cast<int64_t>(B) * (H / 8);
+    const int grid = static_cast<int>(std::min<int64_t>((work + 255) / 256, ctx->num_sms * 4));
+    B2_CUDA(b2_launch(gather_rows_kernel, dim3(grid), dim3(256), 0, s, static_cast<const uint16_t*>(h), ldh, row_index, B, H,
+                      reinterpret_cast<uint16_t*>(ctx->gather_rows)));
+    A = ctx->gather_rows;
+    lda = H;
+  }
+  GemmArgs args{};
+  args.sample_keys = ctx->sample_keys;
+  args.temperatures = temperatures;
+  args.seed = seed;
+  args.vocab_offset = rank * Vr;
+  args.dstate = ctx->dstate;
+  rc = launch_gemm<EPI_SAMPLE>(ctx, A, lda, W, ldw, B, Vr, H, args, 0, s);
+  if (rc != B2_OK) return rc;
+  B2_CUDA(b2_launch(sample_finish_kernel, dim3(1), dim3(256), 0, s, rank, world, B, ctx->cfg.max_seqs, ctx->sample_keys,
+                    reinterpret_cast<unsigned long long*>(ctx->peer[0] + ctx->off_keybox),
+                    reinterpret_cast<unsigned int*>(ctx->peer[0] + ctx->off_flags), ctx->dstate, ctx->status_dev,
+                    static_cast<uint64_t>(ctx->cfg.timeout_ms) * 1000000ull, tokens_out));
+  return B2_OK;
+}
+
+// The fused sampler's noise for one (vocab id, token row, call): host copy of the device arithmetic, for tests.
+int b2_sampler_noise_bits(uint64_t seed, uint32_t vocab_id, uint32_t token, uint32_t call, uint32_t* bits) {
+  if (bits == nullptr) return B2_ERR_ARG;
+  uint32_t r[4] = {vocab_id, token >> 2, call, SAMPLE_TAG};
+  philox4x32_10(r, static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
+  *bits = r[token & 3];
+  return B2_OK;
+}
+
+// Philox4x32-10 itself (counter and key as given), for the known-answer test.
+int b2_philox4x32_10(const uint32_t counter[4], const uint32_t key[2], uint32_t out[4]) {
+  if (counter == nullptr || key == nullptr || out == nullptr) return B2_ERR_ARG;
+  uint32_t r[4] = {counter[0], counter[1], counter[2], counter[3]};
+  philox4x32_10(r, key[0], key[1]);
+  for (int i = 0; i < 4; ++i) out[i] = r[i];
   return B2_OK;
 }
 
@@ -1702,7 +1930,7 @@ extern "C" int b2_gemm_static_scratch(const void* A, int64_t lda, const void* W,
 static_assert(sizeof(b2_gemm_plan) == sizeof(GemmPlan), "b2_gemm_plan mirrors GemmPlan");
 
 extern "C" int b2_plan_gemm(int epilogue, int M, int N, int K, int num_sms, const int* resident_clusters, b2_gemm_plan* plan) {
-  if (plan == nullptr || epilogue < EPI_STORE || epilogue > EPI_PUSH2) return B2_ERR_ARG;
+  if (plan == nullptr || epilogue < EPI_STORE || epilogue > EPI_SAMPLE) return B2_ERR_ARG;
   GemmPlan p{};
   const int min_grid = epilogue == EPI_PUSH ? M : 0;  // the one-shot launch also wants a CTA per token row for its reduce phase
   const int rc = plan_gemm(epilogue, M, N, K, num_sms, min_grid, 0, 1 << 20, resident_clusters != nullptr,

@@ -10,6 +10,7 @@ in token lists and block tables (every rank must be given the same batch).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -19,6 +20,8 @@ from ..layers.sampler import Sampler
 from ..models.qwen3 import Qwen3ForCausalLM
 from ..runtime import get_runtime, init_runtime, shutdown_runtime
 from ..utils.context import reset_context, set_context
+
+FUSED_SAMPLER_MAX_ROWS = 256  # b2_lm_head_sample takes one token tile of the feature-lane layout
 
 
 @dataclass
@@ -77,13 +80,16 @@ class ModelRunner:
     def __init__(self, config: ModelConfig, *, max_num_seqs: int = 512, max_model_len: int = 4096, max_num_batched_tokens: int = 16384,
                  kvcache_block_size: int = 256, num_kvcache_blocks: int | None = None, gpu_memory_utilization: float = 0.9,
                  enforce_eager: bool = False, oneshot_tokens: int = 1024, timeout_ms: int = 5000, seed: int = 0,
-                 full_weights: dict | None = None):
+                 full_weights: dict | None = None, fused_sampler: bool | None = None, sample_seed: int = 0):
         assert dist.is_initialized(), "create the process group first (world size 1 included), as the reference does"
         self.config = config
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
         self.block_size = kvcache_block_size
         self.max_num_seqs, self.max_model_len, self.max_num_batched_tokens = max_num_seqs, max_model_len, max_num_batched_tokens
         self.enforce_eager = enforce_eager
+        # LM head and sampler in one pass (no [B, vocab] logits, no gather); B2_FUSED_SAMPLER=0 keeps them apart
+        self.fused_sampler = (os.environ.get("B2_FUSED_SAMPLER", "1") != "0") if fused_sampler is None else fused_sampler
+        self.sample_seed = sample_seed
         self.device = torch.device("cuda", torch.cuda.current_device())
         # symmetric buffers exist before the layers are built, so graph capture sees fixed addresses
         self.runtime = init_runtime(max_tokens=max_num_batched_tokens, hidden=config.hidden_size, oneshot_tokens=oneshot_tokens,
@@ -177,10 +183,14 @@ class ModelRunner:
     # ---- forward ---------------------------------------------------------------
     @torch.inference_mode()
     def run_model(self, input_ids: torch.Tensor, positions: torch.Tensor, is_prefill: bool):
+        return self.model.compute_logits(self.run_hidden(input_ids, positions, is_prefill))
+
+    def run_hidden(self, input_ids: torch.Tensor, positions: torch.Tensor, is_prefill: bool):
+        """The model forward up to the final norm (eager for prefill, a graph replay for decode)."""
         from ..utils.context import get_context
         n = input_ids.size(0)
         if is_prefill or self.enforce_eager or n > self.graph_bs[-1]:
-            return self.model.compute_logits(self.model(input_ids, positions))
+            return self.model(input_ids, positions)
         ctx = get_context()
         bs = next(b for b in self.graph_bs if b >= n)
         gv = self.graph_vars
@@ -192,7 +202,7 @@ class ModelRunner:
         gv["context_lens"][:n] = ctx.context_lens
         gv["block_tables"][:n, :ctx.block_tables.size(1)] = ctx.block_tables
         self.graphs[bs].replay()
-        return self.model.compute_logits(gv["outputs"][:n])
+        return gv["outputs"][:n]
 
     def _decode_staging(self):
         """Pinned host mirrors of the graphs' input buffers, allocated once: a decode step fills them with
@@ -229,23 +239,28 @@ class ModelRunner:
         gv["block_tables"][:n, :width].copy_(stage["block_tables"][:n, :width], non_blocking=True)
         self.graphs[bs].replay()
         set_context(False)  # the LM head only needs to know this is not a prefill step
-        return self.model.compute_logits(gv["outputs"][:n])
+        return gv["outputs"][:n]
 
     @torch.inference_mode()
     def step(self, seqs: list[Seq], is_prefill: bool, temperatures: list[float] | None = None, num_new: list[int] | None = None):
         """One forward pass + sampling on rank 0; the chosen token ids are
         returned on every rank.  temperatures=None means greedy (argmax)."""
         if not is_prefill and not self.enforce_eager and len(seqs) <= self.graph_bs[-1]:
-            logits = self._decode_graph_step(seqs)
+            hidden = self._decode_graph_step(seqs)
         else:
             ids, pos = self.prepare_prefill(seqs, num_new) if is_prefill else self.prepare_decode(seqs)
-            logits = self.run_model(ids, pos, is_prefill)
+            hidden = self.run_hidden(ids, pos, is_prefill)
         picked = torch.zeros(len(seqs), dtype=torch.int64, device=self.device)
-        if self.rank == 0:
-            if temperatures is None:
-                picked = Sampler.greedy(logits)
-            else:
-                picked = self.sampler(logits, self._h2d(temperatures, torch.float32))
+        if self.fused_sampler and len(seqs) <= FUSED_SAMPLER_MAX_ROWS:
+            temps = None if temperatures is None else self._h2d(temperatures, torch.float32)
+            self.model.sample_tokens(hidden, temps, self.sample_seed, out=picked)
+        else:
+            logits = self.model.compute_logits(hidden)
+            if self.rank == 0:
+                if temperatures is None:
+                    picked = Sampler.greedy(logits)
+                else:
+                    picked = self.sampler(logits, self._h2d(temperatures, torch.float32))
         if self.world > 1:
             from .. import ops
             ops.broadcast_tokens(picked)  # rank 0's choice reaches every rank on the device
@@ -316,9 +331,13 @@ class ResidentDecoder:
     def _body(self):
         r, bs, gv = self.r, self.bs, self.r.graph_vars
         set_context(False, slot_mapping=gv["slot_mapping"][:bs], context_lens=gv["context_lens"][:bs], block_tables=gv["block_tables"][:bs])
-        logits = r.model.compute_logits(r.model(gv["input_ids"][:bs], gv["positions"][:bs]))
-        if r.rank == 0:
-            self.ops.argmax(logits, self.tokens)
+        hidden = r.model(gv["input_ids"][:bs], gv["positions"][:bs])
+        if r.fused_sampler and bs <= FUSED_SAMPLER_MAX_ROWS:
+            r.model.sample_tokens(hidden, None, r.sample_seed, out=self.tokens)  # greedy: rank 0 gets the picks
+        else:
+            logits = r.model.compute_logits(hidden)
+            if r.rank == 0:
+                self.ops.argmax(logits, self.tokens)
         if r.world > 1:
             self.ops.broadcast_tokens(self.tokens)
         self.ops.advance_decode(self.tokens, gv["input_ids"], gv["positions"], gv["context_lens"], gv["slot_mapping"],

@@ -46,3 +46,10 @@ class ParallelLMHead(VocabParallelEmbedding):
     def forward(self, x: torch.Tensor):
         ctx = get_context()
         return ops.lm_head(x, self.weight, ctx.last_token_index if ctx.is_prefill else None)
+
+    def forward_sample(self, x: torch.Tensor, temperatures: torch.Tensor | None, seed: int, out: torch.Tensor | None = None):
+        """forward() followed by Sampler.forward (nanovllm/layers/sampler.py:7-12; greedy when temperatures is
+        None) without materialising the logits: every rank scans its vocabulary slice in the GEMM epilogue and
+        only the best (score, id) per row reaches rank 0.  Returns int64 token ids, valid on rank 0."""
+        ctx = get_context()
+        return ops.lm_head_sample(x, self.weight, ctx.last_token_index if ctx.is_prefill else None, temperatures, seed, out)

@@ -154,6 +154,10 @@ class Qwen3ForCausalLM(nn.Module):
     def compute_logits(self, hidden_states: torch.Tensor):
         return self.lm_head(hidden_states)
 
+    def sample_tokens(self, hidden_states: torch.Tensor, temperatures: torch.Tensor | None, seed: int, out: torch.Tensor | None = None):
+        """compute_logits + the sampler in one pass (token ids valid on rank 0); see ParallelLMHead.forward_sample."""
+        return self.lm_head.forward_sample(hidden_states, temperatures, seed, out)
+
     def load_full_weights(self, weights: dict[str, torch.Tensor]) -> None:
         """Feed full (unsharded) tensors under HF names through every
         parameter's weight_loader, as nanovllm/utils/loader.py:12-28 does for a

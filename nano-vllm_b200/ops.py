@@ -259,6 +259,29 @@ def lm_head(h: torch.Tensor, w: torch.Tensor, row_index: torch.Tensor | None):
     return view
 
 
+def lm_head_sample(h: torch.Tensor, w: torch.Tensor, row_index: torch.Tensor | None, temperatures: torch.Tensor | None,
+                   seed: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """LM head and sampler in one pass over the vocabulary shard (no logits in memory).  Returns int64 token ids
+    [B], valid on rank 0 only.  temperatures: fp32 [B] on the device, or None for greedy decoding."""
+    rt = get_runtime()
+    h2 = _as2d(_bf16_rows(h, "lm_head input"))
+    if h2.stride(0) % 8 != 0 or h2.data_ptr() % 16 != 0:
+        h2 = h2.contiguous()
+    B = h2.shape[0] if row_index is None else row_index.numel()
+    if row_index is not None:
+        assert row_index.dtype == torch.int32 and row_index.is_cuda
+    if temperatures is not None:
+        assert temperatures.dtype == torch.float32 and temperatures.is_cuda and temperatures.is_contiguous() and temperatures.numel() >= B
+    if out is None:
+        out = torch.empty(B, dtype=torch.int64, device=h.device)
+    assert out.dtype == torch.int64 and out.is_cuda and out.numel() >= B
+    Vr, H = w.shape
+    _abi.check(_lib.b2_lm_head_sample(rt.ctx, h2.data_ptr(), h2.stride(0), row_index.data_ptr() if row_index is not None else None,
+                                      w.data_ptr(), w.stride(0), B, Vr, H, temperatures.data_ptr() if temperatures is not None else None,
+                                      int(seed) & 0xFFFFFFFFFFFFFFFF, out.data_ptr(), _stream()), "b2_lm_head_sample")
+    return out[:B]
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     assert logits.dim() == 2 and logits.dtype == torch.bfloat16 and logits.stride(1) == 1
     if out is None:

@@ -203,6 +203,64 @@ def parallel_lm_head(h: torch.Tensor, w_shards: list[torch.Tensor], last_indices
 # --------------------------------------------------------------------------
 
 
+# --------------------------------------------------------------------------
+# sampler
+# --------------------------------------------------------------------------
+
+
+def sampler_with_noise(logits: torch.Tensor, temperatures: torch.Tensor, noise: torch.Tensor) -> torch.Tensor:
+    """nanovllm/layers/sampler.py:9-11 with the exponential noise passed in instead of drawn:
+    probs = softmax(float(logits) / T); token = argmax(probs / clamp_min(E, 1e-10))."""
+    scaled = logits.float() / temperatures.float().unsqueeze(1)
+    probs = torch.softmax(scaled, dim=-1)
+    return (probs / noise.float().clamp_min(1e-10)).argmax(dim=-1)
+
+
+def sampler_scores(logits: torch.Tensor, temperatures: torch.Tensor | None, noise: torch.Tensor | None) -> torch.Tensor:
+    """The same draw without the softmax: the denominator of softmax is common to a row and log is monotone, so
+    argmax_i p_i / E_i = argmax_i (logit_i / T - log E_i).  Returns the fp64 scores whose row-wise argmax is the
+    token; this is the form the fused LM-head sampler evaluates shard by shard.  temperatures None = greedy."""
+    z = logits.float().double()
+    if temperatures is None:
+        return z
+    return z / temperatures.double().unsqueeze(1) - torch.log(noise.double().clamp_min(1e-10))
+
+
+_PHILOX_M0, _PHILOX_M1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
+_PHILOX_W0, _PHILOX_W1 = 0x9E3779B9, 0xBB67AE85
+SAMPLE_TAG = 0x53414D50
+
+
+def philox4x32_10(counter: np.ndarray, key: tuple[int, int]) -> np.ndarray:
+    """Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC'11), vectorised:
+    counter uint32 [..., 4] -> uint32 [..., 4].  Each round: (hi0, lo0) = M0 * c0, (hi1, lo1) = M1 * c2,
+    c = (hi1 ^ c1 ^ k0, lo1, hi0 ^ c3 ^ k1, lo0), then the key is bumped by the Weyl constants."""
+    c = [counter[..., i].astype(np.uint64) for i in range(4)]
+    k0, k1 = key[0] & 0xFFFFFFFF, key[1] & 0xFFFFFFFF
+    mask = np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0, p1 = _PHILOX_M0 * c[0], _PHILOX_M1 * c[2]
+        c = [(p1 >> np.uint64(32)) ^ c[1] ^ np.uint64(k0), p1 & mask, (p0 >> np.uint64(32)) ^ c[3] ^ np.uint64(k1), p0 & mask]
+        k0, k1 = (k0 + _PHILOX_W0) & 0xFFFFFFFF, (k1 + _PHILOX_W1) & 0xFFFFFFFF
+    return np.stack(c, axis=-1).astype(np.uint32)
+
+
+def fused_sampler_noise(seed: int, call: int, rows: int, vocab: int) -> torch.Tensor:
+    """The Exp(1) noise the fused LM-head sampler uses in call number `call`: [rows, vocab] fp64.
+    Counter = (vocab id, row // 4, call, tag), key = seed; word row % 4 of the output; 23 bits -> u in (0, 1)."""
+    v = np.arange(vocab, dtype=np.uint32)
+    out = np.empty((rows, vocab), dtype=np.float64)
+    for grp in range((rows + 3) // 4):
+        ctr = np.stack([v, np.full_like(v, grp), np.full_like(v, call & 0xFFFFFFFF), np.full_like(v, SAMPLE_TAG)], axis=-1)
+        r = philox4x32_10(ctr, (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF))
+        for i in range(4):
+            row = grp * 4 + i
+            if row < rows:
+                u = ((r[:, i] >> np.uint32(9)).astype(np.float64) + 0.5) * 2.0 ** -23
+                out[row] = -np.log(u)
+    return torch.from_numpy(out)
+
+
 def store_kvcache(key: np.ndarray, value: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, slot_mapping: np.ndarray) -> None:
     """nanovllm/layers/attention.py:10-30,33-40, on raw 16-bit words.
 

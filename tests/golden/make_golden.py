@@ -157,6 +157,18 @@ def worker(rank: int, ref_path: str, port: int, out_dir: str):
         out.update({"rope/pos": pos, "rope/q": q, "rope/k": k, "rope/q_out": q2.clone(), "rope/k_out": k2.clone(),
                     "rope/cache": rope.cos_sin_cache.squeeze(1).clone(), "rope/norm_w": hn.weight.data.clone(), "rope/q_normed": qn.clone()})
 
+        # ---- the sampler (the reference runs it on rank 0; the CPU generator is seeded, and the noise it is
+        #      about to draw is recorded by drawing the same tensor from the same seed first) ----------------
+        from nanovllm.layers.sampler import Sampler
+        g = torch.Generator().manual_seed(45)
+        logits = (torch.randn(12, 2048, generator=g) * 3).bfloat16()
+        temps = torch.tensor([0.3, 0.6, 0.6, 0.8, 1.0, 1.0, 1.2, 1.5, 0.05, 2.0, 0.7, 0.9])
+        torch.manual_seed(777)
+        noise = torch.empty(12, 2048).exponential_(1)
+        torch.manual_seed(777)
+        tokens = Sampler()(logits.clone(), temps)
+        out.update({"sampler/logits": logits, "sampler/temperatures": temps, "sampler/noise": noise, "sampler/tokens": tokens.clone()})
+
     dist.barrier()
     if rank == 0:
         groups: dict[str, dict[str, torch.Tensor]] = {}

@@ -39,3 +39,18 @@ def ulp_mismatch_fraction(got: torch.Tensor, ref: torch.Tensor, ulps: int = 1) -
     a = torch.where(a < 0, -(a & 0x7FFF), a)
     b = torch.where(b < 0, -(b & 0x7FFF), b)
     return ((a - b).abs() > ulps).float().mean().item()
+
+
+def check_sampler_picks(tokens, logits, temps, noise, what):
+    """tokens must be the row-wise argmax of the oracle's scores computed from the stored logits, up to ties inside
+    one bf16 ulp of a logit (the two GEMM launches may round a split tile's sum differently)."""
+    from oracle import tp_path as O
+    z = O.sampler_scores(logits.cpu(), temps.cpu() if temps is not None else None, noise)
+    best = z.max(-1).values
+    picked = z.gather(1, tokens.cpu().view(-1, 1)).squeeze(1)
+    lg = logits.float().cpu().double()
+    inv_t = 1.0 if temps is None else (1.0 / temps.cpu().double())
+    slack = 2.0 ** -7 * (lg.abs().max(-1).values) * inv_t + 1e-4
+    assert (picked >= best - slack).all(), f"{what}: a pick is below the best score by {(best - picked).max().item():.4f}"
+    exact = (tokens.cpu() == z.argmax(-1)).float().mean().item()
+    assert exact >= 0.9, f"{what}: only {exact * 100:.0f}% of the rows pick the oracle's token"

@@ -131,6 +131,25 @@ def _worker(rank: int, world: int, port: int):
             dist.barrier()  # rank 0 has read the buffer before anyone writes it again
         rt.check_status()
 
+        # ---- LM head fused with the sampler: each rank scans its vocabulary slice, only (score, id) per row travels ----
+        from tests.gpu_util import check_sampler_picks
+        logits = ops.lm_head(h.to(dev), shard, None)
+        torch.cuda.synchronize()
+        logits = logits.clone() if rank == 0 else None
+        dist.barrier()
+        temps = (torch.rand(40, generator=g) + 0.3).to(dev)
+        for call, t in enumerate([None, temps, temps, None]):
+            buf = torch.full((40,), -7, dtype=torch.int64, device=dev)
+            ops.lm_head_sample(h.to(dev), shard, None, t, 99, out=buf)
+            ops.broadcast_tokens(buf)            # rank 0's picks to everyone (and the exchange that separates two sampler calls)
+            torch.cuda.synchronize()
+            if rank == 0:
+                check_sampler_picks(buf, logits, t, O.fused_sampler_noise(99, call, 40, vocab) if t is not None else None, f"fused sampler call {call}")
+            everyone = [None] * world
+            dist.all_gather_object(everyone, buf.tolist())
+            assert all(e == everyone[0] for e in everyone), "token broadcast after the fused sampler"
+        rt.check_status()
+
         # ---- token broadcast ----
         for step in range(3):
             buf = (torch.arange(64, device=dev) * (step + 1) + 5) if rank == 0 else torch.zeros(64, dtype=torch.int64, device=dev)

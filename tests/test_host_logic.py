@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 # ---- the GEMM launch planner (the library's own arithmetic, read through b2_plan_gemm) ----
-EPI_STORE, EPI_PUSH, EPI_PUSH2 = 0, 1, 2
+EPI_STORE, EPI_PUSH, EPI_PUSH2, EPI_SAMPLE = 0, 1, 2, 3
 SMS = 148
 # clusters of S CTAs resident at once, per tile width: [S] for 32-token tiles, [9 + S] for 64-token tiles.  On a GPU
 # the library asks the occupancy calculator; these stand for a 148-SM part whose clusters of 3, 5, 6 and 7 pack badly
@@ -95,6 +95,7 @@ PLAN_SHAPES = [
     (EPI_PUSH, 64, 4096, 4096), (EPI_PUSH, 64, 5120, 1024), (EPI_PUSH, 64, 5120, 3200), (EPI_PUSH, 256, 5120, 1024), (EPI_PUSH, 1, 1024, 384),
     (EPI_PUSH2, 128, 5120, 1024), (EPI_PUSH2, 1024, 5120, 3200), (EPI_PUSH2, 8192, 5120, 1024), (EPI_PUSH2, 16384, 4096, 2048),
     (EPI_PUSH2, 300, 1024, 1536),
+    (EPI_SAMPLE, 64, 151936, 4096), (EPI_SAMPLE, 64, 18992, 4096), (EPI_SAMPLE, 256, 4096, 1024), (EPI_SAMPLE, 3, 512, 128),
 ]
 
 
@@ -106,6 +107,8 @@ def test_planner_covers_every_unit_once(pkg, epi, m, n, k):
     assert plan.swap == (1 if (epi != EPI_PUSH2 and m <= 256) else 0)
     if epi == EPI_PUSH2:
         assert plan.grid == SMS and plan.cluster_split == 0
+    if epi == EPI_SAMPLE:
+        assert plan.cluster_split == 0 and plan.tiles_q == 1      # the fused sampler runs in the stream-K kernel, one token tile
     check_plan(_abi, plan, m, n, k)
 
 
@@ -130,13 +133,13 @@ def test_planner_choices_for_the_decode_shapes(pkg):
     assert (p.cluster_split, p.gemm_ctas, p.grid) == (0, 1, 128)  # the launch keeps a CTA per token row for the reduce phase
     rc, p = plan_gemm(_abi, EPI_PUSH, 64, 5120, 1024)             # one-shot at decode size: the cluster kernel reduces too
     assert (p.tiles_p, p.cluster_split, p.grid) == (40, 3, 120)
-    for bad in [(0, 0, 64, 64), (0, 64, 0, 64), (0, 64, 64, 0), (3, 64, 64, 64)]:
+    for bad in [(0, 0, 64, 64), (0, 64, 0, 64), (0, 64, 64, 0), (4, 64, 64, 64), (-1, 64, 64, 64)]:
         assert plan_gemm(_abi, *bad)[0] == 1                      # B2_ERR_ARG
     assert _abi.lib.b2_plan_gemm(0, 64, 64, 64, SMS, None, None) == 1
 
 
 @settings(max_examples=120, deadline=None)
-@given(epi=st.sampled_from([EPI_STORE, EPI_PUSH, EPI_PUSH2]), m=st.integers(1, 3000), n8=st.integers(1, 1200), k8=st.integers(1, 700),
+@given(epi=st.sampled_from([EPI_STORE, EPI_PUSH, EPI_PUSH2, EPI_SAMPLE]), m=st.integers(1, 3000), n8=st.integers(1, 1200), k8=st.integers(1, 700),
        sms=st.sampled_from([148, 132, 7, 1]))
 def test_planner_property(epi, m, n8, k8, sms):
     import __graft_entry__
