@@ -87,8 +87,12 @@ class ModelRunner:
         self.block_size = kvcache_block_size
         self.max_num_seqs, self.max_model_len, self.max_num_batched_tokens = max_num_seqs, max_model_len, max_num_batched_tokens
         self.enforce_eager = enforce_eager
-        # LM head and sampler in one pass (no [B, vocab] logits, no gather); B2_FUSED_SAMPLER=0 keeps them apart
-        self.fused_sampler = (os.environ.get("B2_FUSED_SAMPLER", "1") != "0") if fused_sampler is None else fused_sampler
+        # LM head and sampler in one pass (no [B, vocab] logits, no gather).  B2_FUSED_SAMPLER=0/1 forces it off/on;
+        # by default it is on at the world sizes it has been run and measured at (1 and 2 GPUs)
+        env = os.environ.get("B2_FUSED_SAMPLER")
+        if fused_sampler is None:
+            fused_sampler = (env != "0") if env is not None else self.world <= 2
+        self.fused_sampler = fused_sampler
         self.sample_seed = sample_seed
         self.device = torch.device("cuda", torch.cuda.current_device())
         # symmetric buffers exist before the layers are built, so graph capture sees fixed addresses
