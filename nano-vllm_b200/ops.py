@@ -40,6 +40,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> 
     w = _bf16_rows(w, "gemm weight")
     M, K = x2.shape
     N = w.shape[0]
+    if w.dim() != 2 or w.shape[1] != K:
+        raise ValueError(f"gemm: input has {K} features, weight is {tuple(w.shape)}")
     out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
     if M:
         _abi.check(_lib.b2_gemm(get_runtime().ctx, x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0),
@@ -56,7 +58,7 @@ def qkv_fused(x: torch.Tensor, w: torch.Tensor, bias, nq: int, nkv: int, head_di
         x2 = x2.contiguous()
     M, K = x2.shape
     N = w.shape[0]
-    assert N == (nq + 2 * nkv) * head_dim
+    assert N == (nq + 2 * nkv) * head_dim and w.shape[1] == K
     assert positions.dtype == torch.int64 and cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
     have_cache = k_cache is not None and k_cache.numel() > 0
     if have_cache:
@@ -84,6 +86,8 @@ def gemm_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor) -> torch.Tensor:
         x2 = x2.contiguous()
     M, K = x2.shape
     I = w_pairs.shape[0] // 2
+    if w_pairs.shape[1] != K or w_pairs.shape[0] % 2:
+        raise ValueError(f"gemm_silu_mul: input has {K} features, paired weight is {tuple(w_pairs.shape)}")
     out = torch.empty(M, I, dtype=torch.bfloat16, device=x.device)
     if M:
         _abi.check(_lib.b2_gemm_silu_mul(get_runtime().ctx, x2.data_ptr(), x2.stride(0), w_pairs.data_ptr(), w_pairs.stride(0),
