@@ -222,6 +222,45 @@ def compare_model_forward(runner, bs: int, iters: int = 20) -> dict:
             "what": "model forward only (embedding, all decoder layers, final norm); LM head and sampling excluded on both sides"}
 
 
+TRACE_PHASES = ["set-up done", "first operand tile landed", "last MMA issued", "earlier kernels complete", "epilogue done",
+                "GEMM part left", "reduce phase done", "kernel entry"]
+
+
+def trace_phases(make_call, warmup: int = 3) -> dict:
+    """Phase stamps of one launch of the fused block on this rank (the library's b2_trace): for every phase the
+    minimum, median and maximum over the CTAs, in microseconds after the first CTA entered the kernel.  Each GPU
+    has its own clock, so only the differences inside one rank mean something."""
+    import ctypes as C
+
+    import numpy as np
+
+    from . import _abi
+    from .runtime import get_runtime
+    rt = get_runtime()
+    for i in range(warmup):
+        make_call(i)
+    torch.cuda.synchronize()
+    _abi.check(_abi.lib.b2_trace(rt.ctx, 1, None, 0), "b2_trace on")
+    make_call(warmup)
+    torch.cuda.synchronize()
+    max_ctas = 256
+    buf = (C.c_ulonglong * (max_ctas * 16))()
+    _abi.check(_abi.lib.b2_trace(rt.ctx, 0, buf, max_ctas), "b2_trace read")
+    ns = np.frombuffer(buf, dtype=np.uint64).reshape(max_ctas, 8, 2)[:, :, 1].astype(np.int64)
+    live = ns[:, 7] > 0
+    out = {"ctas": int(live.sum())}
+    if not live.any():
+        return out
+    t0 = ns[live, 7].min()
+    for i in (7, 0, 3, 1, 2, 4, 5, 6):
+        v = ns[live, i]
+        v = v[v > 0]
+        if len(v):
+            r = (v - t0) / 1e3
+            out[TRACE_PHASES[i]] = [round(float(r.min()), 2), round(float(np.median(r)), 2), round(float(r.max()), 2)]
+    return out
+
+
 def main():
     import argparse
     here = os.path.dirname(os.path.abspath(__file__))
@@ -235,6 +274,7 @@ def main():
     ap.add_argument("--tokens", default="1,8,64,256,1024,8192")
     ap.add_argument("--no-nccl", action="store_true")
     ap.add_argument("--iters", type=int, default=200)
+    ap.add_argument("--trace", action="store_true", help="instead of timing, print every rank's per-phase stamps of one launch per shape")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
@@ -251,6 +291,22 @@ def main():
     try:
         for proj, k_total in (("o_proj", 8192), ("down_proj", 25600)):
             for m in ms:
+                if a.trace:
+                    from nanovllm_b200 import ops
+                    kr = k_total // world
+                    dev = torch.device("cuda", local)
+                    ws = [(torch.randn(5120, kr, device=dev) * 0.02).bfloat16() for _ in range(4)]
+                    x = torch.randn(m, kr, device=dev).bfloat16()
+                    residual = torch.randn(m, 5120, device=dev).bfloat16()
+                    norm_w = (torch.rand(5120, device=dev) + 0.5).bfloat16()
+                    dist.barrier()
+                    stamps = mb.trace_phases(lambda i: ops.rowpar_fused(x, ws[i % 4], None, residual, norm_w, 1e-6))
+                    everyone = [None] * world
+                    dist.all_gather_object(everyone, stamps)
+                    if rank == 0:
+                        for r, st in enumerate(everyone):
+                            print(json.dumps({"proj": proj, "M": m, "Kr": kr, "tp": world, "rank": r} | st), flush=True)
+                    continue
                 res = mb.compare_blocks([(proj, m, 5120, k_total // world)], peaks, iters=a.iters if m <= 1024 else 20, with_nccl=not a.no_nccl)
                 if rank == 0:
                     print(json.dumps(res[proj] | {"proj": proj}), flush=True)
