@@ -75,6 +75,7 @@ SIGNATURES = {
     "b2_plan_gemm": [_i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(GemmPlan)],
     "b2_plan_cta_units": [C.POINTER(GemmPlan), _i, C.POINTER(_i), _i],
     "b2_plan_tile_contributors": [C.POINTER(GemmPlan), _i, C.POINTER(_i), C.POINTER(_i)],
+    "b2_last_gemm_kernel": [],
     "b2_row_owner": [_i, _i, C.POINTER(_i)],
     "b2_owned_rows": [_i, _i, _i],
 }

@@ -205,6 +205,50 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// ---- the same for a CTA pair (cta_group::2): two CTAs of a cluster, ranks 2i and 2i+1, run one 256-row MMA.
+// Every tcgen05 instruction of a kernel must name the same group, so a pair kernel uses only these forms.
+// Allocation and release are issued by the same warp index in BOTH CTAs (each gets the address in its own slot).
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Issued by one thread of the pair's even CTA.  Each CTA contributes the 128 rows of A and half of the rows of B
+// that lie in its own shared memory at the descriptors' offsets; each CTA's tensor memory receives its 128 rows of D.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival on the mbarrier at this shared-memory offset in every CTA of `cta_mask`, once all MMAs issued so far
+// by this thread have completed (a signal, not a data copy).
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(cta_mask) : "memory");
+}
+// 2-D tiled load into THIS CTA's shared memory whose completion bytes are counted on an mbarrier that may live in
+// the pair's other CTA (`bar_cluster` is a shared::cluster address, e.g. from map_to_cta).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* m, uint32_t bar_cluster, int x, int y,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+// arrival on an mbarrier of another CTA of the cluster
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+
 // 32 lanes x 32 consecutive fp32 columns: thread t of the warp receives the 32
 // columns of TMEM lane (lane_base + t).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -243,6 +287,11 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int n) {
          | (1u << 10)                               // B format: BF16
          | (static_cast<uint32_t>(n >> 3) << 17)    // N / 8
          | (static_cast<uint32_t>(128 >> 4) << 24); // M / 16
+}
+
+// The same for a CTA pair: M = 256 (128 rows per CTA), N = n.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16_pair(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
 }
 
 // ---- bf16 packing / data-as-flag helpers --------------------------------------

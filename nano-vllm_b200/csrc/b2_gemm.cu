@@ -1265,6 +1265,212 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
 // ---------------------------------------------------------------------------
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// ---------------------------------------------------------------------------
+// Many tokens (prefill, large two-shot calls): CTA pairs.  Two CTAs of a cluster (ranks 0 and 1) run one
+// tcgen05.mma.cta_group::2 of 256 token rows x BN features: each CTA stages its own 128 rows of the activations
+// and its own half (BN / 2 rows) of the weight tile, the tensor cores of both SMs read the two halves of the
+// weight tile from both shared memories, and each CTA's tensor memory receives its 128 rows of the result.
+// Per SM and K block that is 16 KB + BN * 64 B of operands from L2 instead of 16 KB + BN * 128 B: the token-row
+// GEMM is limited by exactly that traffic.
+//   - every CTA:  TMA producer (warp 0) fills its own stages; completion bytes of both CTAs are counted on the
+//                 even CTA's "full" barrier; 4 epilogue warps drain the CTA's own tensor memory.
+//   - even CTA:   its MMA thread (warp 1) waits on "full", issues the MMAs for the pair, and signals "stage
+//                 free" and "accumulator ready" to both CTAs with multicast commits.
+//   - odd CTA:    its epilogue warps report "accumulator drained" to the even CTA's barrier.
+// Whole 256 x BN tiles are dealt round-robin to the pairs (no K split).  Not yet a default path: it is used only
+// when the environment has B2_PAIR=1.
+// ---------------------------------------------------------------------------
+template <int BN>
+struct CfgPair {
+  static constexpr uint32_t P_BYTES = BM * BK * 2;            // this CTA's 128 token rows
+  static constexpr uint32_t Q_BYTES = (BN / 2) * BK * 2;      // this CTA's half of the weight tile
+  static constexpr uint32_t STAGE_BYTES = P_BYTES + Q_BYTES;
+  static constexpr int ACC = 512 / BN;                        // accumulators in tensor memory (512 columns in all)
+  static constexpr uint32_t TMEM_COLS = 512;
+  static constexpr int STAGES_RAW = (232448 - 1024 - 256 - 4 * STAGING_BYTES_PER_WARP) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 4 * STAGING_BYTES_PER_WARP;
+  static_assert(BN == 128 || BN == 256, "pair tiles are 256 x 128 or 256 x 256");
+  static_assert(2 * STAGES + 2 * ACC <= 30, "barrier area is 256 bytes");
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const GemmArgs a) {
+  using C = CfgPair<BN>;
+  constexpr int STAGES = C::STAGES, ACC = C::ACC;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_base = b2::smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES);
+  const uint32_t bar_full = b2::smem_u32(bars);             // used in the even CTA: bytes of both CTAs' loads
+  const uint32_t bar_empty = bar_full + STAGES * 8;         // in each CTA: its stage may be refilled
+  const uint32_t bar_tfull = bar_empty + STAGES * 8;        // in each CTA: accumulator complete
+  const uint32_t bar_tempty = bar_tfull + ACC * 8;          // used in the even CTA: both CTAs' epilogues have drained it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * ACC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __shared__ float red[NUM_THREADS / 32];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cr = b2::cluster_ctarank();                // 0 = even CTA (issues the MMAs), 1 = odd CTA
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int KB = a.kblocks;
+  const int tiles2 = a.tilesP * a.tilesQ;                   // tilesP counts 256-row tiles here
+  const int my_tiles = pair < tiles2 ? (tiles2 - pair + pairs - 1) / pairs : 0;
+  const int n_units = my_tiles * KB;
+
+  if (threadIdx.x == 0) {
+    stamp(a, 7);
+    b2::tma_prefetch_desc(&tmP);
+    b2::tma_prefetch_desc(&tmQ);
+    for (int s = 0; s < STAGES; ++s) {
+      b2::mbar_init(bar_full + s * 8, 1);
+      b2::mbar_init(bar_empty + s * 8, 1);
+    }
+    for (int i = 0; i < ACC; ++i) {
+      b2::mbar_init(bar_tfull + i * 8, 1);
+      b2::mbar_init(bar_tempty + i * 8, 8);  // 4 epilogue warps of each of the 2 CTAs
+    }
+    *abort_flag = 0;
+    b2::mbar_fence_init();
+  }
+  if (warp == 1) {
+    b2::tmem_alloc_pair(b2::smem_u32(tmem_slot), C::TMEM_COLS);
+    b2::tmem_relinquish_pair();
+  }
+  b2::tc_fence_before();
+  __syncthreads();
+  // the other CTA's barriers must exist before anything is counted on them
+  b2::cluster_arrive();
+  b2::cluster_wait();
+  b2::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) b2::pdl_launch_dependents();
+  if (threadIdx.x == 0) stamp(a, 0);
+  unsigned int parity = 0;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      const uint32_t full0 = b2::map_to_cta(bar_full, 0);   // the even CTA's "full" barriers, as a cluster address
+      const int pre = n_units < STAGES ? n_units : STAGES;
+      int t = pair, kb = 0;                                 // tile and K block of the unit being loaded
+      // weights of the first stages depend on no earlier kernel
+      for (int i = 0; i < pre; ++i) {
+        if (cr == 0) b2::mbar_arrive_expect_tx(bar_full + i * 8, 2 * C::STAGE_BYTES);
+        const int tq = t % a.tilesQ;
+        b2::tma_load_2d_pair(smem_base + i * C::STAGE_BYTES + C::P_BYTES, &tmQ, full0 + i * 8, kb * BK,
+                             tq * BN + static_cast<int>(cr) * (BN / 2), b2::kEvictNormal);
+        if (++kb == KB) { kb = 0; t += pairs; }
+      }
+      b2::pdl_wait();
+      stamp(a, 3);
+      t = pair;
+      kb = 0;
+      for (int i = 0; i < pre; ++i) {
+        const int tp = t / a.tilesQ;
+        b2::tma_load_2d_pair(smem_base + i * C::STAGE_BYTES, &tmP, full0 + i * 8, kb * BK, (tp * 2 + static_cast<int>(cr)) * BM,
+                             b2::kEvictNormal);
+        if (++kb == KB) { kb = 0; t += pairs; }
+      }
+      int stage = pre == STAGES ? 0 : pre;
+      uint32_t phase = pre == STAGES ? 1 : 0;
+      for (int i = pre; i < n_units; ++i) {
+        if (!b2::mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_SMEM_EMPTY)) break;
+        if (cr == 0) b2::mbar_arrive_expect_tx(bar_full + stage * 8, 2 * C::STAGE_BYTES);
+        const int tp = t / a.tilesQ, tq = t - tp * a.tilesQ;
+        const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
+        b2::tma_load_2d_pair(dst, &tmP, full0 + stage * 8, kb * BK, (tp * 2 + static_cast<int>(cr)) * BM, b2::kEvictNormal);
+        b2::tma_load_2d_pair(dst + C::P_BYTES, &tmQ, full0 + stage * 8, kb * BK, tq * BN + static_cast<int>(cr) * (BN / 2),
+                             b2::kEvictNormal);
+        if (++kb == KB) { kb = 0; t += pairs; }
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (even CTA only) ----------------
+    if (lane == 0 && cr == 0) {
+      constexpr uint32_t idesc = b2::umma_idesc_bf16_pair(BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int j = 0; ok && j < my_tiles; ++j) {
+        const int acc = j % ACC;
+        const uint32_t use = static_cast<uint32_t>(j / ACC);
+        if (!b2::mbar_wait(bar_tempty + acc * 8, (use & 1) ^ 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_TMEM_EMPTY)) break;
+        b2::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!b2::mbar_wait(bar_full + stage * 8, phase, abort_flag, PIPE_LIMIT_NS, B2_WAIT_SMEM_FULL)) { ok = false; break; }
+          if (j == 0 && kb == 0) stamp(a, 1);
+          b2::tc_fence_after();
+          const uint32_t sp = smem_base + stage * C::STAGE_BYTES;
+          const uint64_t dp = b2::umma_smem_desc(sp);
+          const uint64_t dq = b2::umma_smem_desc(sp + C::P_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) b2::umma_bf16_pair(d_tmem, dp + 2 * k, dq + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          b2::umma_commit_pair(bar_empty + stage * 8, 3);   // both CTAs may refill this stage
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        b2::umma_commit_pair(bar_tfull + acc * 8, 3);       // both CTAs may drain their half of the accumulator
+      }
+      stamp(a, 2);
+    }
+  } else {
+    // ---------------- epilogue warps (both CTAs) ----------------
+    const int q = warp & 3;
+    unsigned char* wbuf = smem + STAGES * C::STAGE_BYTES + 256 + q * STAGING_BYTES_PER_WARP;
+    const uint32_t tempty0 = b2::map_to_cta(bar_tempty, 0);
+    b2::pdl_wait();
+    if (is_push(EPI)) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
+    for (int j = 0; j < my_tiles; ++j) {
+      const int t = pair + j * pairs;
+      const int acc = j % ACC;
+      const uint32_t use = static_cast<uint32_t>(j / ACC);
+      if (!b2::mbar_wait(bar_tfull + acc * 8, use & 1, abort_flag, PIPE_LIMIT_NS, B2_WAIT_TMEM_FULL)) break;
+      b2::tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      const int tp = t / a.tilesQ, tq = t - tp * a.tilesQ;
+      const int p_row = (tp * 2 + static_cast<int>(cr)) * BM + q * 32 + lane;  // token row of this lane
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        b2::tmem_ld_32x32(taddr + c * 32, r);
+        b2::tc_wait_ld();
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        emit_chunk<BN, false, EPI>(a, v, p_row, tq * BN, c, lane, parity, wbuf, 0u, nullptr);
+      }
+      b2::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) b2::mbar_arrive_cluster(tempty0 + acc * 8);
+    }
+    if (warp == 2 && lane == 0) stamp(a, 4);
+  }
+
+  // ---- all roles of both CTAs meet; tensor memory goes back ------------------
+  b2::pdl_wait();
+  if (is_push(EPI)) parity = *reinterpret_cast<volatile unsigned int*>(&a.dstate->rowpar_seq) & 1u;
+  __syncwarp();
+  b2::tc_fence_before();
+  __syncthreads();
+  const int aborted = *abort_flag;
+  if (aborted) {
+    // let bulk copies that may still be in flight (this CTA's and the other's) land before anyone leaves
+    for (int i = 0; i < 100; ++i) __nanosleep(2000);
+    if (threadIdx.x == 0) b2::report_timeout(a.status, aborted);
+  }
+  // neither CTA may free the pair's tensor memory or leave while the other still signals its barriers
+  b2::cluster_arrive();
+  b2::cluster_wait();
+  b2::tc_fence_after();
+  if (warp == 1) b2::tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+
+  fused_tail<EPI>(a, parity, red, abort_flag, aborted);
+}
+
 template <int BN, bool SWAP, int EPI>
 int launch_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmArgs& args, int grid, cudaStream_t stream) {
   static bool configured = false;
@@ -1288,6 +1494,25 @@ int launch_cluster_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Ge
   B2_CUDA(b2_launch_cluster(gemm_cluster_kernel<BN, EPI>, dim3(tiles * S), dim3(NUM_THREADS), CfgCluster<BN>::SMEM_BYTES, stream,
                             static_cast<unsigned>(S), tmP, tmQ, args));
   return B2_OK;
+}
+
+template <int BN, int EPI>
+int launch_pair_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmArgs& args, int grid, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    B2_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, CfgPair<BN>::SMEM_BYTES));
+    configured = true;
+  }
+  B2_CUDA(b2_launch_cluster(gemm_pair_kernel<BN, EPI>, dim3(grid), dim3(NUM_THREADS), CfgPair<BN>::SMEM_BYTES, stream, 2u, tmP, tmQ, args));
+  return B2_OK;
+}
+
+bool pair_path_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("B2_PAIR");
+    return e != nullptr && e[0] == '1';
+  }();
+  return on;
 }
 
 // How many clusters of S CTAs of the cluster kernel can be resident at once (cached per BN and S).
@@ -1321,7 +1546,7 @@ int max_resident_clusters(int S) {
   return n;
 }
 
-thread_local int g_last_gemm_path = 0;  // 0 = stream-K kernel, 1 = cluster kernel (set by launch_gemm)
+thread_local int g_last_gemm_path = 0;  // 0 = stream-K kernel, 1 = cluster kernel, 2 = CTA-pair kernel (set by launch_gemm)
 
 bool cluster_path_enabled() {
   static const bool on = [] {
@@ -1441,6 +1666,20 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
   if (rc != B2_OK) return rc;
 
   g_last_gemm_path = 0;
+  if constexpr (EPI == EPI_STORE || EPI == EPI_PUSH2) {
+    // CTA pairs (tcgen05.mma.cta_group::2) for many-token problems; opt-in until measured: B2_PAIR=1
+    if (pair_path_enabled() && !swap && bn >= 128 && M >= 512 && ctx->num_sms >= 2) {
+      CUtensorMap tmQh;
+      rc = b2::encode_tmap_2d(&tmQh, pQ, K, rowsQ, ldQ, BK, bn / 2);
+      if (rc != B2_OK) return rc;
+      args.tilesP = (M + 2 * BM - 1) / (2 * BM);
+      args.gemm_ctas = ctx->num_sms & ~1;
+      args.round_robin = 1;
+      g_last_gemm_path = 2;
+      if (bn == 128) return launch_pair_inst<128, EPI>(tmP, tmQh, args, args.gemm_ctas, stream);
+      return launch_pair_inst<256, EPI>(tmP, tmQh, args, args.gemm_ctas, stream);
+    }
+  }
   if constexpr (EPI == EPI_STORE || EPI == EPI_PUSH) {
     if (plan.cluster_split > 0) {
       g_last_gemm_path = 1;
@@ -1997,6 +2236,8 @@ extern "C" int b2_plan_tile_contributors(const b2_gemm_plan* plan, int tile, int
   }
   return B2_OK;
 }
+
+extern "C" int b2_last_gemm_kernel(void) { return g_last_gemm_path; }
 
 extern "C" int b2_row_owner(int token, int world, int* local_row) {
   if (token < 0 || world < 1 || local_row == nullptr) return -B2_ERR_ARG;

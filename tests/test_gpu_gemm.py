@@ -202,3 +202,39 @@ def test_lm_head_single_rank(ops, rt):
     assert logits.shape == (4, 151936)
     assert_close_bf16(logits, h[idx.long()].float() @ w.float().t(), "lm_head prefill (last tokens)")
     assert torch.equal(ops.argmax(logits).cpu(), logits.float().argmax(-1).cpu())
+
+
+PAIR_SCRIPT = r"""
+import sys, torch
+sys.path.insert(0, %(root)r)
+import __graft_entry__ as entry
+entry.load_package()
+from tests.gpu_util import assert_close_bf16, ensure_group
+ensure_group()
+from nanovllm_b200 import ops, _abi
+from nanovllm_b200.runtime import init_runtime, shutdown_runtime
+rt = init_runtime(max_tokens=8192, hidden=5120, oneshot_tokens=1024, timeout_ms=2000)
+for (m, n, k) in [(512, 256, 64), (512, 512, 256), (1000, 1032, 520), (1024, 5120, 1024), (777, 128, 1024), (4096, 4096, 4096)]:
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.02).bfloat16()
+    y = ops.gemm(x.cuda(), w.cuda())
+    used = _abi.lib.b2_last_gemm_kernel()
+    torch.cuda.synchronize()
+    rt.check_status()
+    assert used == 2, (m, n, k, used)
+    assert_close_bf16(y, x.float() @ w.float().t(), f"pair gemm {m}x{n}x{k}")
+    print("ok", m, n, k, flush=True)
+shutdown_runtime()
+"""
+
+
+@pytest.mark.skipif(os.environ.get("B2_TEST_PAIR") != "1", reason="the CTA-pair GEMM is opt-in (B2_PAIR=1) until it has been measured; set B2_TEST_PAIR=1 to run it")
+def test_pair_kernel_opt_in():
+    """The tcgen05.mma.cta_group::2 kernel, in a child process whose environment switches it on."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, B2_PAIR="1", MASTER_PORT="29547")
+    res = subprocess.run([sys.executable, "-c", PAIR_SCRIPT % {"root": root}], env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
