@@ -337,6 +337,10 @@ typedef struct b2_gemm_plan {
  * [9 + S] for 64-token tiles = clusters of S CTAs the device holds at once
  * (on a GPU the library asks the occupancy calculator). */
 int b2_plan_gemm(int epilogue, int M, int N, int K, int num_sms, const int* resident_clusters, b2_gemm_plan* plan);
+/* The same with planner options: bit 0 = one whole tile per CTA when a many-token problem fits one wave (what the
+ * environment variable B2_WHOLE_TILES=1 switches on for the library's own launches). */
+int b2_plan_gemm_opts(int epilogue, int M, int N, int K, int num_sms, const int* resident_clusters, int options,
+                      b2_gemm_plan* plan);
 
 /* The K blocks CTA `cta` computes under `plan`, in order, as triples
  * (tile, k_block, starts_segment) written to units[3 * cap].  Returns their

@@ -73,6 +73,7 @@ SIGNATURES = {
     "b2_advance_decode": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _p],
     # the planner as data: no CUDA call, usable without a GPU
     "b2_plan_gemm": [_i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(GemmPlan)],
+    "b2_plan_gemm_opts": [_i, _i, _i, _i, _i, C.POINTER(_i), _i, C.POINTER(GemmPlan)],
     "b2_plan_cta_units": [C.POINTER(GemmPlan), _i, C.POINTER(_i), _i],
     "b2_plan_tile_contributors": [C.POINTER(GemmPlan), _i, C.POINTER(_i), C.POINTER(_i)],
     "b2_last_gemm_kernel": [],

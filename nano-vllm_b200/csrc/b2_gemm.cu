@@ -1593,13 +1593,38 @@ int pick_cluster_split(int bn, int tiles, int kblocks, int num_sms, Resident&& r
 }
 
 // Pure host arithmetic: no CUDA call besides what `resident` makes.
+constexpr int PLAN_WHOLE_TILES = 1;  // planner option, see whole_tiles_enabled()
+
+// B2_WHOLE_TILES=1 (opt-in until measured): a token-row problem whose tiles fit the device in one wave at some tile
+// width runs one whole tile per CTA instead of a stream-K split, whose fp32 combine in L2 costs more than the idle SMs
+// when the GEMM itself lasts a few microseconds (128-512 tokens of a two-shot call).
+bool whole_tiles_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("B2_WHOLE_TILES");
+    return e != nullptr && e[0] == '1';
+  }();
+  return on;
+}
+
 template <class Resident>
 int plan_gemm(int epi, int M, int N, int K, int num_sms, int min_grid, int reducers, int64_t tile_cap, bool clusters_on,
-              Resident&& resident, GemmPlan& p) {
+              Resident&& resident, GemmPlan& p, int options = 0) {
   if (M <= 0 || N <= 0 || K <= 0 || num_sms <= 0) return B2_ERR_ARG;
   p.swap = (epi != EPI_PUSH2) && M <= 256;
   if (p.swap) p.bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   else p.bn = (N >= 256) ? 256 : (N > 64 ? 128 : 64);
+  bool one_tile_per_cta = false;
+  if (!p.swap && (options & PLAN_WHOLE_TILES)) {
+    const int sms = epi == EPI_PUSH2 ? std::max(1, num_sms - reducers) : num_sms;
+    for (int bn = 64; bn <= p.bn; bn *= 2) {  // the narrowest tile that still fits one wave gives the most parallelism
+      const int64_t t = static_cast<int64_t>((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+      if (t <= sms) {
+        p.bn = bn;
+        one_tile_per_cta = true;
+        break;
+      }
+    }
+  }
   const int rowsP = p.swap ? N : M, rowsQ = p.swap ? M : N;
   p.tilesP = (rowsP + BM - 1) / BM;
   p.tilesQ = (rowsQ + p.bn - 1) / p.bn;
@@ -1615,6 +1640,10 @@ int plan_gemm(int epi, int M, int N, int K, int num_sms, int min_grid, int reduc
   g = std::min<int64_t>(g, U);
   p.gemm_ctas = static_cast<int>(g);
   p.round_robin = (!p.swap && tiles >= 4 * g) ? 1 : 0;
+  if (one_tile_per_cta) {
+    p.gemm_ctas = static_cast<int>(tiles);
+    p.round_robin = 1;
+  }
   p.grid = (epi == EPI_PUSH2) ? num_sms : std::max(p.gemm_ctas, std::min(min_grid, num_sms));
   p.cluster_split = 0;
   if ((epi == EPI_STORE || epi == EPI_PUSH) && clusters_on && p.swap && p.tilesQ == 1 && p.bn <= 64) {  // up to 64 tokens: the decode sizes
@@ -1637,7 +1666,7 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
                               if constexpr (EPI == EPI_PUSH2 || EPI == EPI_SAMPLE) return 0;
                               else return bn == 32 ? max_resident_clusters<32, EPI>(S) : max_resident_clusters<64, EPI>(S);
                             },
-                            plan);
+                            plan, whole_tiles_enabled() ? PLAN_WHOLE_TILES : 0);
   if (prc != B2_OK) return prc;
   const bool swap = plan.swap != 0;
   const int bn = plan.bn;
@@ -2169,11 +2198,16 @@ extern "C" int b2_gemm_static_scratch(const void* A, int64_t lda, const void* W,
 static_assert(sizeof(b2_gemm_plan) == sizeof(GemmPlan), "b2_gemm_plan mirrors GemmPlan");
 
 extern "C" int b2_plan_gemm(int epilogue, int M, int N, int K, int num_sms, const int* resident_clusters, b2_gemm_plan* plan) {
+  return b2_plan_gemm_opts(epilogue, M, N, K, num_sms, resident_clusters, 0, plan);
+}
+
+extern "C" int b2_plan_gemm_opts(int epilogue, int M, int N, int K, int num_sms, const int* resident_clusters, int options,
+                                 b2_gemm_plan* plan) {
   if (plan == nullptr || epilogue < EPI_STORE || epilogue > EPI_SAMPLE) return B2_ERR_ARG;
   GemmPlan p{};
   const int min_grid = epilogue == EPI_PUSH ? M : 0;  // the one-shot launch also wants a CTA per token row for its reduce phase
   const int rc = plan_gemm(epilogue, M, N, K, num_sms, min_grid, 0, 1 << 20, resident_clusters != nullptr,
-                           [&](int bn, int S) { return resident_clusters[(bn == 32 ? 0 : 9) + S]; }, p);
+                           [&](int bn, int S) { return resident_clusters[(bn == 32 ? 0 : 9) + S]; }, p, options);
   if (rc != B2_OK) return rc;
   plan->swap = p.swap;
   plan->bn = p.bn;

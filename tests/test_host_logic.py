@@ -30,6 +30,12 @@ def plan_gemm(abi, epi, m, n, k, sms=SMS, resident=RESIDENT):
     return rc, plan
 
 
+def plan_gemm_opts(abi, epi, m, n, k, options, sms=SMS):
+    plan = abi.GemmPlan()
+    rc = abi.lib.b2_plan_gemm_opts(epi, m, n, k, sms, (C.c_int * 18)(*RESIDENT), options, C.byref(plan))
+    return rc, plan
+
+
 def cta_units(abi, plan, cta):
     cap = 4096
     buf = (C.c_int * (3 * cap))()
@@ -136,6 +142,27 @@ def test_planner_choices_for_the_decode_shapes(pkg):
     for bad in [(0, 0, 64, 64), (0, 64, 0, 64), (0, 64, 64, 0), (4, 64, 64, 64), (-1, 64, 64, 64)]:
         assert plan_gemm(_abi, *bad)[0] == 1                      # B2_ERR_ARG
     assert _abi.lib.b2_plan_gemm(0, 64, 64, 64, SMS, None, None) == 1
+
+
+@pytest.mark.parametrize("epi,m,n,k", [(EPI_PUSH2, 256, 5120, 1024), (EPI_PUSH2, 512, 5120, 3200), (EPI_STORE, 300, 4096, 4096),
+                                       (EPI_PUSH2, 1024, 5120, 1024), (EPI_STORE, 8192, 5120, 1024)])
+def test_whole_tile_option(pkg, epi, m, n, k):
+    """Planner option 1 (B2_WHOLE_TILES=1): a many-token problem that fits one wave of tiles at some tile width gets one
+    whole tile per CTA - nothing is split, so no fp32 combine - and everything else is planned as before."""
+    from nanovllm_b200 import _abi
+    rc, base = plan_gemm(_abi, epi, m, n, k)
+    rc2, opt = plan_gemm_opts(_abi, epi, m, n, k, 1)
+    assert rc == 0 and rc2 == 0
+    check_plan(_abi, opt, m, n, k)
+    row_tiles = (m + 127) // 128
+    fits = [bn for bn in (64, 128, 256) if bn <= base.bn and row_tiles * ((n + bn - 1) // bn) <= SMS]
+    if base.swap or not fits:
+        assert [getattr(opt, f) for f, _ in opt._fields_] == [getattr(base, f) for f, _ in base._fields_]
+    else:
+        assert opt.bn == fits[0] and opt.round_robin == 1 and opt.gemm_ctas == opt.tiles_p * opt.tiles_q
+        for cta in range(opt.gemm_ctas):
+            units = cta_units(_abi, opt, cta)
+            assert [u[:2] for u in units] == [(cta, kb) for kb in range(opt.kblocks)]
 
 
 @settings(max_examples=120, deadline=None)
