@@ -78,6 +78,23 @@ int b2_ctx_destroy(b2_ctx* ctx);
 int b2_status(b2_ctx* ctx, int* code, int* detail);
 int b2_status_clear(b2_ctx* ctx);
 
+/* After B2_ERR_TIMEOUT the context is poisoned on EVERY rank: an abandoned
+ * launch leaves partial sums in the split-K workspace, counters that are not
+ * back at zero, partial rows in the peers' inboxes, and launch-sequence
+ * numbers that may differ between ranks.  b2_status_clear clears only the
+ * word; later collective calls on the same context may return wrong sums.
+ * Either destroy and re-create the context on all ranks, or call
+ * b2_ctx_reset on all ranks: it synchronises the device, puts every buffer,
+ * counter and sequence number of this rank back to its initial state and
+ * clears the status word.  No rank may have a b2_* kernel in flight: the
+ * caller brackets the call with host barriers (all ranks idle -> barrier ->
+ * b2_ctx_reset -> barrier -> resume).  The reference has no counterpart: a
+ * hung NCCL collective there ends the process
+ * (nanovllm/engine/model_runner.py:50-59 is reached only on a clean exit).
+ * Not for use during graph capture; captured graphs stay valid (addresses do
+ * not change). */
+int b2_ctx_reset(b2_ctx* ctx);
+
 /* Phase tracing of the GEMM / fused row-parallel kernel (the reference has
  * only per-step wall-clock in nanovllm/engine/llm_engine.py:72-83).  While
  * enabled, every CTA of those kernels records 8 (SM clock, global ns) stamps:
@@ -285,12 +302,16 @@ int b2_broadcast_tokens(b2_ctx* ctx, int64_t* buf, int n, void* stream);
  *      (nanovllm/engine/model_runner.py:172-188) -------------------------------
  * For i < n: input_ids[i] = tokens[i]; positions[i] += 1; context_lens[i] += 1;
  * slot_mapping[i] = block_tables[i, positions[i] / block_size] * block_size
- *                   + positions[i] % block_size.  block_tables int32 with row
- * stride bt_stride.  Lets consecutive decode steps run without a host round
- * trip. */
+ *                   + positions[i] % block_size.  block_tables int32 with
+ * bt_width columns and row stride bt_stride.  Lets consecutive decode steps
+ * run without a host round trip.  A row that has run out of room - its next
+ * position lies past the table's width, its table entry is -1, the slot would
+ * be >= num_slots (slots in the KV cache), or its slot already is -1 (a padded
+ * or frozen row) - is frozen: slot_mapping[i] = -1 (it stores no K/V), its
+ * position and context length stay as they are. */
 int b2_advance_decode(const int64_t* tokens, int64_t* input_ids, int64_t* positions, int32_t* context_lens,
-                      int32_t* slot_mapping, const int32_t* block_tables, int64_t bt_stride, int block_size,
-                      int n, void* stream);
+                      int32_t* slot_mapping, const int32_t* block_tables, int64_t bt_stride, int bt_width,
+                      int block_size, int64_t num_slots, int n, void* stream);
 
 /* ---- elementwise neighbours of the path (the reference generates these with
  *      torch.compile -> Triton) ----------------------------------------------

@@ -51,6 +51,7 @@ SIGNATURES = {
     "b2_ctx_destroy": [_p],
     "b2_status": [_p, C.POINTER(_i), C.POINTER(_i)],
     "b2_status_clear": [_p],
+    "b2_ctx_reset": [_p],
     "b2_trace": [_p, _i, _p, _i],
     "b2_gemm": [_p, _p, _i64, _p, _i64, _p, _p, _i64, _i, _i, _i, _p],
     "b2_qkv_fused": [_p, _p, _i64, _p, _i64, _p, _p, _i64, _i, _i, _i, _i, _i, _p, _p, _f, _p, _p, _p, _p, _p, _p],
@@ -70,7 +71,7 @@ SIGNATURES = {
     "b2_qk_norm_rope_store": [_p, _i64, _i, _i, _i, _i, _p, _p, _f, _p, _p, _p, _p, _p, _p],
     "b2_argmax": [_p, _i64, _i, _i, _p, _p],
     "b2_broadcast_tokens": [_p, _p, _i, _p],
-    "b2_advance_decode": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _p],
+    "b2_advance_decode": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _i64, _i, _p],
     # the planner as data: no CUDA call, usable without a GPU
     "b2_plan_gemm": [_i, _i, _i, _i, _i, C.POINTER(_i), C.POINTER(GemmPlan)],
     "b2_plan_gemm_opts": [_i, _i, _i, _i, _i, C.POINTER(_i), _i, C.POINTER(GemmPlan)],

@@ -89,6 +89,17 @@ int64_t b2_launch_count(void) { return g_launches.load(); }
 
 static int ctx_init(b2_ctx* c);
 
+// Data-as-flag buffers start out "not written" (the sentinel), flags and counters at zero, the token inbox at -1.
+static int init_symmetric_region(b2_ctx* c) {
+  const size_t words = c->off_logits / 4;
+  b2_fill_u32_kernel<<<1024, 256>>>(reinterpret_cast<uint32_t*>(c->symm), words, B2_SENTINEL32);
+  b2::count_launch();
+  B2_CUDA(cudaGetLastError());
+  B2_CUDA(cudaMemset(c->symm + c->off_logits, 0, c->off_tokens - c->off_logits));
+  B2_CUDA(cudaMemset(c->symm + c->off_tokens, 0xFF, c->symm_bytes - c->off_tokens));
+  return B2_OK;
+}
+
 int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
   if (cfg == nullptr || out == nullptr) return B2_ERR_ARG;
   *out = nullptr;
@@ -141,14 +152,9 @@ static int ctx_init(b2_ctx* c) {
   off = align_up(off + 2 * static_cast<size_t>(c->cfg.max_seqs > 0 ? c->cfg.max_seqs : 1) * 8, 1024);
   c->symm_bytes = off;
   B2_CUDA(cudaMalloc(&c->symm, c->symm_bytes));
-  // data-as-flag buffers start out "not written"; flags start at zero
   {
-    const size_t words = c->off_logits / 4;
-    b2_fill_u32_kernel<<<1024, 256>>>(reinterpret_cast<uint32_t*>(c->symm), words, B2_SENTINEL32);
-    b2::count_launch();
-    B2_CUDA(cudaGetLastError());
-    B2_CUDA(cudaMemset(c->symm + c->off_logits, 0, c->off_tokens - c->off_logits));
-    B2_CUDA(cudaMemset(c->symm + c->off_tokens, 0xFF, c->symm_bytes - c->off_tokens));
+    const int rc = init_symmetric_region(c);
+    if (rc != B2_OK) return rc;
   }
   for (int r = 0; r < B2_MAX_WORLD; ++r) c->peer[r] = nullptr;
   c->peer[c->cfg.rank] = c->symm;
@@ -239,6 +245,22 @@ int b2_trace(b2_ctx* c, int enable, unsigned long long* host_out, int max_ctas) 
     B2_CUDA(cudaMemset(c->trace, 0, static_cast<size_t>(c->num_sms) * 16 * sizeof(unsigned long long)));
   }
   c->trace_on = enable != 0;
+  return B2_OK;
+}
+
+int b2_ctx_reset(b2_ctx* c) {
+  if (c == nullptr) return B2_ERR_ARG;
+  B2_CUDA(cudaSetDevice(c->cfg.device));
+  B2_CUDA(cudaDeviceSynchronize());
+  const int rc = init_symmetric_region(c);
+  if (rc != B2_OK) return rc;
+  B2_CUDA(cudaMemset(c->splitk_ws, 0, c->splitk_ws_bytes));
+  B2_CUDA(cudaMemset(c->tile_counters, 0, static_cast<size_t>(c->tile_counter_cap) * 4 * sizeof(int)));
+  B2_CUDA(cudaMemset(c->dstate, 0, sizeof(B2DeviceState)));
+  if (c->sample_keys) B2_CUDA(cudaMemset(c->sample_keys, 0, static_cast<size_t>(c->cfg.max_seqs) * 8));
+  B2_CUDA(cudaDeviceSynchronize());
+  c->status_host->code = 0;
+  c->status_host->detail = 0;
   return B2_OK;
 }
 

@@ -429,20 +429,30 @@ __global__ void __launch_bounds__(256) broadcast_tokens_kernel(const BcastArgs a
   }
 }
 
+// A row whose next position has no block in its table (past the table's width, a -1 entry, or a slot beyond the
+// cache) is frozen: it stores nothing (slot -1) and its position and context length stay, so that a replay past
+// a sequence's capacity can never send the KV scatter outside the cache.
 __global__ void advance_decode_kernel(const int64_t* __restrict__ tokens, int64_t* __restrict__ input_ids,
                                       int64_t* __restrict__ positions, int32_t* __restrict__ context_lens,
                                       int32_t* __restrict__ slot_mapping, const int32_t* __restrict__ block_tables,
-                                      int64_t bt_stride, int block_size, int n) {
+                                      int64_t bt_stride, int bt_width, int block_size, int64_t num_slots, int n) {
   b2::pdl_launch_dependents();
   b2::pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   input_ids[i] = tokens[i];
   const int64_t p = positions[i] + 1;
+  const int64_t b = p / block_size;
+  int32_t blk = -1;
+  if (p >= 0 && b < bt_width && slot_mapping[i] >= 0) blk = block_tables[i * bt_stride + b];
+  const int64_t slot = static_cast<int64_t>(blk) * block_size + (p % block_size);
+  if (blk < 0 || slot >= num_slots) {
+    slot_mapping[i] = -1;
+    return;
+  }
   positions[i] = p;
   context_lens[i] += 1;
-  const int32_t blk = block_tables[i * bt_stride + p / block_size];
-  slot_mapping[i] = blk * block_size + static_cast<int32_t>(p % block_size);
+  slot_mapping[i] = static_cast<int32_t>(slot);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -582,12 +592,13 @@ int b2_broadcast_tokens(b2_ctx* ctx, int64_t* buf, int n, void* stream) {
 }
 
 int b2_advance_decode(const int64_t* tokens, int64_t* input_ids, int64_t* positions, int32_t* context_lens,
-                      int32_t* slot_mapping, const int32_t* block_tables, int64_t bt_stride, int block_size, int n, void* stream) {
-  if (n < 0 || block_size <= 0) return B2_ERR_ARG;
+                      int32_t* slot_mapping, const int32_t* block_tables, int64_t bt_stride, int bt_width, int block_size,
+                      int64_t num_slots, int n, void* stream) {
+  if (n < 0 || block_size <= 0 || bt_width <= 0 || bt_stride < bt_width || num_slots <= 0) return B2_ERR_ARG;
   if (n == 0) return B2_OK;
   if (!tokens || !input_ids || !positions || !context_lens || !slot_mapping || !block_tables) return B2_ERR_ARG;
   B2_CUDA(b2_launch(advance_decode_kernel, dim3((n + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream), tokens, input_ids, positions,
-                    context_lens, slot_mapping, block_tables, bt_stride, block_size, n));
+                    context_lens, slot_mapping, block_tables, bt_stride, bt_width, block_size, num_slots, n));
   return B2_OK;
 }
 

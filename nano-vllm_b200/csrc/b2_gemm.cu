@@ -1265,6 +1265,26 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
 // ---------------------------------------------------------------------------
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Function attributes (the opt-in to more than 48 KB of dynamic shared memory) and occupancy answers belong to
+// a device, not to the process: one flag per device ordinal, set under a lock.
+constexpr int MAX_DEVICES = 64;
+std::mutex g_config_mutex;
+struct PerDeviceOnce {
+  bool done[MAX_DEVICES] = {};
+  // runs `configure` the first time it is asked for the current device; returns B2_OK or its error
+  template <class F>
+  int ensure(F&& configure) {
+    int dev = 0;
+    B2_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) return b2::set_error(B2_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+    std::lock_guard<std::mutex> lock(g_config_mutex);
+    if (done[dev]) return B2_OK;
+    const int rc = configure();
+    if (rc == B2_OK) done[dev] = true;
+    return rc;
+  }
+};
+
 // ---------------------------------------------------------------------------
 // Many tokens (prefill, large two-shot calls): CTA pairs.  Two CTAs of a cluster (ranks 0 and 1) run one
 // tcgen05.mma.cta_group::2 of 256 token rows x BN features: each CTA stages its own 128 rows of the activations
@@ -1473,24 +1493,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant_
 
 template <int BN, bool SWAP, int EPI>
 int launch_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmArgs& args, int grid, cudaStream_t stream) {
-  static bool configured = false;
+  static PerDeviceOnce configured;
   constexpr uint32_t smem_bytes = SWAP ? Cfg<BN>::SMEM_BYTES : Cfg<BN>::SMEM_BYTES_ROWS;
   static_assert(smem_bytes <= 232448, "more shared memory than an SM has");
-  if (!configured) {
+  const int crc = configured.ensure([&]() -> int {
     B2_CUDA(cudaFuncSetAttribute(gemm_kernel<BN, SWAP, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-    configured = true;
-  }
+    return B2_OK;
+  });
+  if (crc != B2_OK) return crc;
   B2_CUDA(b2_launch(gemm_kernel<BN, SWAP, EPI>, dim3(grid), dim3(NUM_THREADS), smem_bytes, stream, tmP, tmQ, args));
   return B2_OK;
 }
 
 template <int BN, int EPI>
-int launch_cluster_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmArgs& args, int tiles, int S, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+int configure_cluster_kernel() {
+  static PerDeviceOnce configured;
+  return configured.ensure([&]() -> int {
     B2_CUDA(cudaFuncSetAttribute(gemm_cluster_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, CfgCluster<BN>::SMEM_BYTES));
-    configured = true;
-  }
+    return B2_OK;
+  });
+}
+
+template <int BN, int EPI>
+int launch_cluster_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmArgs& args, int tiles, int S, cudaStream_t stream) {
+  const int crc = configure_cluster_kernel<BN, EPI>();
+  if (crc != B2_OK) return crc;
   B2_CUDA(b2_launch_cluster(gemm_cluster_kernel<BN, EPI>, dim3(tiles * S), dim3(NUM_THREADS), CfgCluster<BN>::SMEM_BYTES, stream,
                             static_cast<unsigned>(S), tmP, tmQ, args));
   return B2_OK;
@@ -1498,11 +1525,12 @@ int launch_cluster_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Ge
 
 template <int BN, int EPI>
 int launch_pair_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmArgs& args, int grid, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  const int crc = configured.ensure([&]() -> int {
     B2_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, CfgPair<BN>::SMEM_BYTES));
-    configured = true;
-  }
+    return B2_OK;
+  });
+  if (crc != B2_OK) return crc;
   B2_CUDA(b2_launch_cluster(gemm_pair_kernel<BN, EPI>, dim3(grid), dim3(NUM_THREADS), CfgPair<BN>::SMEM_BYTES, stream, 2u, tmP, tmQ, args));
   return B2_OK;
 }
@@ -1515,17 +1543,24 @@ bool pair_path_enabled() {
   return on;
 }
 
-// How many clusters of S CTAs of the cluster kernel can be resident at once (cached per BN and S).
+// How many clusters of S CTAs of the cluster kernel can be resident at once (cached per device, BN and S).
 template <int BN, int EPI>
 int max_resident_clusters(int S) {
-  static int cache[9] = {0, -1, -1, -1, -1, -1, -1, -1, -1};
+  static int cache[MAX_DEVICES][9];
+  static bool cache_init = false;
   if (S < 1 || S > 8) return 0;
-  if (cache[S] >= 0) return cache[S];
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(gemm_cluster_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, CfgCluster<BN>::SMEM_BYTES) != cudaSuccess) return 0;
-    configured = true;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return 0;
+  {
+    std::lock_guard<std::mutex> lock(g_config_mutex);
+    if (!cache_init) {
+      for (auto& row : cache)
+        for (int& v : row) v = -1;
+      cache_init = true;
+    }
+    if (cache[dev][S] >= 0) return cache[dev][S];
   }
+  if (configure_cluster_kernel<BN, EPI>() != B2_OK) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(S * 64);
   cfg.blockDim = dim3(NUM_THREADS);
@@ -1542,7 +1577,8 @@ int max_resident_clusters(int S) {
     cudaGetLastError();
     n = 0;
   }
-  cache[S] = n;
+  std::lock_guard<std::mutex> lock(g_config_mutex);
+  cache[dev][S] = n;
   return n;
 }
 

@@ -330,6 +330,7 @@ class ResidentDecoder:
         with torch.cuda.graph(self.graph, runner.graph_pool):
             self._body()
         torch.cuda.synchronize()
+        self.replays_left = 0  # nothing loaded yet
 
     @torch.inference_mode()
     def _body(self):
@@ -345,7 +346,7 @@ class ResidentDecoder:
         if r.world > 1:
             self.ops.broadcast_tokens(self.tokens)
         self.ops.advance_decode(self.tokens, gv["input_ids"], gv["positions"], gv["context_lens"], gv["slot_mapping"],
-                                gv["block_tables"], r.block_size)
+                                gv["block_tables"][:bs], r.block_size, r.num_kvcache_blocks * r.block_size)
         reset_context()
 
     @torch.inference_mode()
@@ -355,13 +356,21 @@ class ResidentDecoder:
         assert n == self.bs
         bs = r.block_size
         width = max(len(s.block_table) for s in seqs)
+        assert width <= gv["block_tables"].shape[1], "a block table is longer than max_model_len allows"
+        assert all(len(s) <= len(s.block_table) * bs for s in seqs), "a sequence is longer than its block table"
         gv["input_ids"][:n] = r._h2d([s.token_ids[-1] for s in seqs], torch.int64)
         gv["positions"][:n] = r._h2d([len(s) - 1 for s in seqs], torch.int64)
         gv["context_lens"][:n] = r._h2d([len(s) for s in seqs], torch.int32)
         gv["slot_mapping"][:n] = r._h2d([s.block_table[(len(s) - 1) // bs] * bs + (len(s) - 1) % bs for s in seqs], torch.int32)
-        gv["block_tables"][:n, :width] = r._h2d([s.block_table + [0] * (width - len(s.block_table)) for s in seqs], torch.int32)
+        gv["block_tables"][:n].fill_(-1)  # columns past a sequence's own blocks: no room (the advance kernel freezes such a row)
+        gv["block_tables"][:n, :width] = r._h2d([s.block_table + [-1] * (width - len(s.block_table)) for s in seqs], torch.int32)
+        # replays until the first sequence has filled its last block: each replay stores the K/V of one more position
+        self.replays_left = min(len(s.block_table) * bs - len(s) for s in seqs) + 1
 
     def replay(self) -> None:
+        if self.replays_left <= 0:
+            raise RuntimeError("ResidentDecoder.replay: a sequence has filled the blocks it was loaded with; load() a batch with more blocks")
+        self.replays_left -= 1
         self.graph.replay()
 
 

@@ -9,8 +9,6 @@ varlen kernel for prefill and its paged kv-cache kernel for decode.
 """
 from __future__ import annotations
 
-import os
-
 import torch
 from torch import nn
 
@@ -58,24 +56,9 @@ def _sdpa_paged(q, k_cache, v_cache, context_lens, block_tables, scale, q_lens=N
     return torch.cat(outs)
 
 
-_TRTLLM_WORKSPACE: dict = {}
-
-
-def _trtllm_decode(q, k_cache, v_cache, context_lens, block_tables, scale):
-    """Decode attention through the flashinfer package's Blackwell kernels (another library call on the same paged
-    cache tensors; opt-in with B2_ATTENTION=trtllm, to be compared with flash-attn's sm_80-class kernel)."""
-    from flashinfer.decode import trtllm_batch_decode_with_kv_cache
-    ws = _TRTLLM_WORKSPACE.get(q.device)
-    if ws is None:
-        ws = _TRTLLM_WORKSPACE[q.device] = torch.zeros(128 << 20, dtype=torch.uint8, device=q.device)
-    max_seq_len = block_tables.shape[1] * k_cache.shape[1]
-    return trtllm_batch_decode_with_kv_cache(q.contiguous(), (k_cache, v_cache), ws, block_tables, context_lens, max_seq_len,
-                                             bmm1_scale=scale, bmm2_scale=1.0, kv_layout="NHD")
-
-
 class Attention(nn.Module):
-    # "flash_attn" (the reference's library call), "sdpa" (tests on small shapes), or "trtllm" (decode only, opt-in)
-    backend = os.environ.get("B2_ATTENTION", "flash_attn")
+    # "flash_attn" (the reference's library call) or "sdpa" (plain PyTorch, for tests on small shapes when flash-attn cannot run)
+    backend = "flash_attn"
 
     def __init__(self, num_heads, head_dim, scale, num_kv_heads):
         super().__init__()
@@ -110,8 +93,6 @@ class Attention(nn.Module):
             return flash_attn_varlen_func(q, k, v, max_seqlen_q=ctx.max_seqlen_q, cu_seqlens_q=ctx.cu_seqlens_q,
                                           max_seqlen_k=ctx.max_seqlen_k, cu_seqlens_k=ctx.cu_seqlens_k,
                                           softmax_scale=self.scale, causal=True, block_table=ctx.block_tables)
-        if Attention.backend == "trtllm":
-            return _trtllm_decode(q, k_cache, v_cache, ctx.context_lens, ctx.block_tables, self.scale)
         return flash_attn_with_kvcache(q.unsqueeze(1), k_cache, v_cache, cache_seqlens=ctx.context_lens,
                                        block_table=ctx.block_tables, softmax_scale=self.scale, causal=True).squeeze(1)
 

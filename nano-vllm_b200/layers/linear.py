@@ -84,30 +84,61 @@ class ColumnParallelLinear(LinearBase):
 class MergedColumnParallelLinear(ColumnParallelLinear):
     """Several column-parallel matrices stacked along the output dimension
     (gate_proj and up_proj).  Shard `i` of a checkpoint tensor lands at row
-    offset sum(output_sizes[:i]) / tp_size of the local weight."""
+    offset sum(output_sizes[:i]) / tp_size of the local weight.
+
+    `pair_rows()` (before loading) switches the stored layout to the one the
+    fused gate_up + SiLU*mul GEMM reads: the two matrices' rows interleaved
+    (row 2j = first matrix's row j, row 2j+1 = second matrix's row j).  The
+    loader then writes each shard straight into its rows, so no second copy of
+    the weight exists; `forward` still returns [first | second] columns."""
 
     def __init__(self, input_size: int, output_sizes: list[int], bias: bool = False):
         self.output_sizes = list(output_sizes)
+        self.paired = False
         super().__init__(input_size, sum(output_sizes), bias)
 
+    def pair_rows(self) -> "MergedColumnParallelLinear":
+        assert len(self.output_sizes) == 2 and self.output_sizes[0] == self.output_sizes[1] and self.bias is None
+        self.paired = True
+        self._pairs = None
+        return self
+
     def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor, loaded_shard_id: int):
-        offset = sum(self.output_sizes[:loaded_shard_id]) // self.tp_size
-        size = self.output_sizes[loaded_shard_id] // self.tp_size
-        param.data.narrow(self.tp_dim, offset, size).copy_(self._shard_of(loaded_weight, self.tp_dim))
+        shard = self._shard_of(loaded_weight, self.tp_dim)
+        if self.paired:
+            param.data[loaded_shard_id::2].copy_(shard)
+        else:
+            offset = sum(self.output_sizes[:loaded_shard_id]) // self.tp_size
+            size = self.output_sizes[loaded_shard_id] // self.tp_size
+            param.data.narrow(self.tp_dim, offset, size).copy_(shard)
         self._pairs = None
 
     _pairs: torch.Tensor | None = None
 
     def paired_weight(self) -> torch.Tensor:
-        """The local weight with the two halves' rows interleaved (row 2j = first half's row j, row 2j+1 = second
-        half's row j): the layout ops.gemm_silu_mul reads.  Built once from `weight` (which keeps the reference's
-        [first half ; second half] layout) the first time it is asked for; costs a second copy of the weight."""
+        """The local weight with the two halves' rows interleaved: the layout ops.gemm_silu_mul reads.  With
+        pair_rows() it is `weight` itself; otherwise a second copy built once from the reference's
+        [first half ; second half] layout the first time it is asked for."""
+        if self.paired:
+            return self.weight.data
         if self._pairs is None:
             assert len(self.output_sizes) == 2 and self.output_sizes[0] == self.output_sizes[1] and self.bias is None
             half = self.weight.shape[0] // 2
             w = self.weight.data
             self._pairs = torch.stack((w[:half], w[half:]), dim=1).reshape(2 * half, w.shape[1]).contiguous()
         return self._pairs
+
+    def reference_weight(self) -> torch.Tensor:
+        """The local weight in the reference's layout [first half ; second half] (a copy when the rows are paired)."""
+        if not self.paired:
+            return self.weight.data
+        return torch.cat((self.weight.data[0::2], self.weight.data[1::2]), dim=0)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = ops.gemm(x, self.weight, self.bias)
+        if self.paired:  # columns come out as (first_0, second_0, first_1, ...): back to [first | second]
+            y = torch.cat((y[..., 0::2], y[..., 1::2]), dim=-1)
+        return y
 
     def forward_silu_mul(self, x: torch.Tensor) -> torch.Tensor:
         """SiLU(first half) * second half of forward(x), in the GEMM's epilogue."""

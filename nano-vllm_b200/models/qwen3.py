@@ -77,7 +77,8 @@ class Qwen3MLP(nn.Module):
     def __init__(self, hidden_size: int, intermediate_size: int, hidden_act: str) -> None:
         super().__init__()
         assert hidden_act == "silu"
-        self.gate_up_proj = MergedColumnParallelLinear(hidden_size, [intermediate_size] * 2, bias=False)
+        # rows stored interleaved (gate_j, up_j): the layout the fused gate_up + SiLU*mul launch reads, filled by the loader
+        self.gate_up_proj = MergedColumnParallelLinear(hidden_size, [intermediate_size] * 2, bias=False).pair_rows()
         self.down_proj = RowParallelLinear(intermediate_size, hidden_size, bias=False)
         self.act_fn = SiluAndMul()
 

@@ -302,10 +302,13 @@ def broadcast_tokens(buf: torch.Tensor) -> torch.Tensor:
     return buf
 
 
-def advance_decode(tokens, input_ids, positions, context_lens, slot_mapping, block_tables, block_size: int) -> None:
-    """Device-side equivalent of building the next decode step's inputs."""
+def advance_decode(tokens, input_ids, positions, context_lens, slot_mapping, block_tables, block_size: int, num_slots: int) -> None:
+    """Device-side equivalent of building the next decode step's inputs.  num_slots = slots of the KV cache
+    (blocks * block_size): a row whose next position has no block, or whose slot would lie outside the cache, is
+    frozen (slot -1, position and length unchanged) instead of being sent outside the cache."""
     n = tokens.numel()
     assert tokens.dtype == torch.int64 and positions.dtype == torch.int64 and block_tables.dtype == torch.int32
+    assert block_tables.dim() == 2 and block_tables.stride(1) == 1 and block_tables.shape[0] >= n
     _abi.check(_lib.b2_advance_decode(tokens.data_ptr(), input_ids.data_ptr(), positions.data_ptr(), context_lens.data_ptr(),
-                                      slot_mapping.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), block_size, n, _stream()),
-               "b2_advance_decode")
+                                      slot_mapping.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), block_tables.shape[1],
+                                      block_size, num_slots, n, _stream()), "b2_advance_decode")

@@ -148,9 +148,8 @@ def compare_model_forward(runner, bs: int, iters: int = 20) -> dict:
             return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).to(x.dtype)
         return rot(q), rot(k)
 
-    def _silu_mul(x):
-        a, b = x.chunk(2, -1)
-        return F.silu(a) * b
+    def _silu_mul(x):  # the model stores gate and up rows interleaved: columns come out as (gate_0, up_0, gate_1, ...)
+        return F.silu(x[..., 0::2]) * x[..., 1::2]
 
     try:
         rms, add_rms, rope, silu_mul = (torch.compile(f) for f in (_rms, lambda x, r, w: _reference_add_rms(x, r, w, eps), _rope, _silu_mul))

@@ -28,6 +28,7 @@ class TPRuntime:
         torch.cuda.set_device(device)
         _abi.check(_abi.lib.b2_ctx_create(C.byref(cfg), C.byref(ctx)), "b2_ctx_create")
         self.ctx = ctx
+        self.poisoned = False
         if world > 1:
             handle = (C.c_ubyte * _abi.HANDLE_BYTES)()
             _abi.check(_abi.lib.b2_symm_export(self.ctx, handle), "b2_symm_export")
@@ -40,11 +41,28 @@ class TPRuntime:
 
     def check_status(self) -> None:
         """Raise if a bounded device-side wait has expired since the last check.
-        No CUDA call is made; call it after the step's own synchronisation."""
+        No CUDA call is made; call it after the step's own synchronisation.
+        After an expired wait the runtime refuses further checks until every
+        rank has called reset() (or the runtime has been re-created): the
+        buffers and launch counters of the ranks no longer agree."""
+        if self.poisoned:
+            raise _abi.B2Error(f"rank {self.rank}: a device-side wait expired earlier; call reset() on every rank")
         code, detail = C.c_int(), C.c_int()
         _abi.lib.b2_status(self.ctx, C.byref(code), C.byref(detail))
         if code.value != _abi.OK:
+            self.poisoned = True
             raise _abi.B2Error(f"rank {self.rank}: {_abi.WAIT_NAMES.get(detail.value, detail.value)} (code {code.value})")
+
+    def reset(self, group=None) -> None:
+        """Collective over the ranks: back to the state right after creation (see b2_ctx_reset).  Every rank must
+        call it, with none of its kernels in flight."""
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=group)
+        _abi.check(_abi.lib.b2_ctx_reset(self.ctx), "b2_ctx_reset")
+        if self.world > 1:
+            dist.barrier(group=group)
+        self.poisoned = False
 
     def close(self) -> None:
         if self.ctx:

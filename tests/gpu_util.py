@@ -5,7 +5,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-TOL_ABS, TOL_REL = 2e-2, 1e-2  # the bf16 tolerance of the path: |err| <= 2e-2 + 1e-2 * max|ref| against an fp32 reference
+TOL_ABS, TOL_REL = 2e-2, 1e-2  # the bf16 tolerance of the path, per element: |got - ref| <= 2e-2 + 1e-2 * |ref| against an fp32 reference
 
 
 def ensure_group():
@@ -15,20 +15,31 @@ def ensure_group():
         dist.init_process_group("gloo", rank=0, world_size=1)
 
 
+def error_stats(got: torch.Tensor, ref_fp32: torch.Tensor) -> dict:
+    """max |err|, max |err| / |ref| over the elements with |ref| >= 1, and the worst ratio err / (abs + rel |ref|)."""
+    got, ref = got.float().cpu(), ref_fp32.float().cpu()
+    err = (got - ref).abs()
+    big = ref.abs() >= 1.0
+    return {"max_abs_err": err.max().item() if err.numel() else 0.0,
+            "max_rel_err": (err[big] / ref.abs()[big]).max().item() if big.any() else 0.0,
+            "worst_vs_bound": (err / (TOL_ABS + TOL_REL * ref.abs())).max().item() if err.numel() else 0.0}
+
+
 def assert_close_bf16(got: torch.Tensor, ref_fp32: torch.Tensor, what: str = "", abs_tol=TOL_ABS, rel_tol=TOL_REL):
+    """Every element within abs_tol + rel_tol * |its own reference value|."""
     got = got.float().cpu()
     ref = ref_fp32.float().cpu()
     assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
     if ref.numel() == 0:
         return
     err = (got - ref).abs()
-    bound = abs_tol + rel_tol * ref.abs().max().item()
-    worst = err.max().item() if err.numel() else 0.0
-    if not worst <= bound:
-        idx = np.unravel_index(int(err.argmax()), err.shape)
-        bad = (err > bound).float().mean().item()
-        raise AssertionError(f"{what}: max abs err {worst:.4e} > {bound:.4e} at {idx} (got {got[idx].item():.5f}, ref {ref[idx].item():.5f}); "
-                             f"{bad * 100:.2f}% of elements out of tolerance")
+    bound = abs_tol + rel_tol * ref.abs()
+    over = err > bound
+    if over.any() or not torch.isfinite(got).all():
+        excess = torch.where(torch.isfinite(err), err - bound, torch.full_like(err, float("inf")))
+        idx = np.unravel_index(int(excess.argmax()), err.shape)
+        raise AssertionError(f"{what}: |err| {err[idx].item():.4e} > {bound[idx].item():.4e} at {idx} (got {got[idx].item():.5f}, ref {ref[idx].item():.5f}); "
+                             f"{over.float().mean().item() * 100:.3f}% of elements out of tolerance; max abs err {err.max().item():.4e}")
 
 
 def ulp_mismatch_fraction(got: torch.Tensor, ref: torch.Tensor, ulps: int = 1) -> float:

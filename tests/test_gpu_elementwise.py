@@ -160,6 +160,22 @@ def test_rope_golden(ops, golden_dir):
     assert torch.equal(qkv[:, 256:384].cpu().view(m, 2, 64), r["k_out"])
 
 
+def test_rotary_embedding_class_forward_golden(pkg, golden_dir):
+    """RotaryEmbedding.forward(positions, query, key), the reference's class surface
+    (nanovllm/layers/rotary_embedding.py:37-48), against the reference's own outputs."""
+    from nanovllm_b200.layers.rotary_embedding import RotaryEmbedding
+    r = torch.load(os.path.join(golden_dir, "rope.pt"))
+    rope = RotaryEmbedding(64, 64, 512, 1e6).to(DEV)
+    assert torch.allclose(rope.cos_sin_cache.cpu(), r["cache"], rtol=0, atol=1e-6)
+    rope.cos_sin_cache.copy_(r["cache"])  # the fixture's table, bit for bit
+    q, k = r["q"].to(DEV), r["k"].to(DEV)
+    q_in, k_in = q.clone(), k.clone()
+    q_out, k_out = rope(r["pos"].to(DEV), q, k)
+    torch.cuda.synchronize()
+    assert torch.equal(q_out.cpu(), r["q_out"]) and torch.equal(k_out.cpu(), r["k_out"])
+    assert torch.equal(q, q_in) and torch.equal(k, k_in)  # inputs untouched, as in the reference
+
+
 def test_embedding_local(ops, golden_dir):
     d = torch.load(os.path.join(golden_dir, "vocab.pt"))
     got = ops.embed(d["ids"].to(DEV), d["w"].to(DEV), 0, d["w"].shape[0], 1)

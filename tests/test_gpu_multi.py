@@ -230,7 +230,22 @@ def _timeout_worker(rank: int, world: int, port: int):
                 rt.check_status()
             # the device is still usable after the expired wait
             assert torch.ones(4, device=dev).sum().item() == 4.0
+            # ... but the context is not, until every rank has reset it
+            with pytest.raises(_abi.B2Error, match="reset"):
+                rt.check_status()
         dist.barrier()  # rank 1 has launched nothing in between
+        # rank 0's abandoned partial rows sit in rank 1's inbox and the ranks' launch counters differ by one:
+        # the collective reset puts both back, and a healthy call gives the right sums again
+        rt.reset()
+        from tests.gpu_util import assert_close_bf16
+        for _ in range(3):
+            normed, new_res = ops.rowpar_fused(xs[rank].to(dev), ws[rank].to(dev), None, residual.to(dev), norm_w.to(dev), 1e-6)
+        torch.cuda.synchronize()
+        rt.check_status()
+        exact_n, exact_s = O.fused_row_parallel_norm_exact(xs, ws, residual, norm_w, 1e-6)
+        assert_close_bf16(normed, exact_n, f"rank {rank}: normed after reset")
+        assert_close_bf16(new_res, exact_s, f"rank {rank}: residual after reset")
+        dist.barrier()
     finally:
         shutdown_runtime()
         dist.destroy_process_group()

@@ -217,6 +217,12 @@ def _loader_worker(rank, world, port, q):
             ok &= torch.equal(row.weight.data, rp[f"w_shard{rank}"])
         ok &= torch.equal(qkv.weight.data, O.shard_qkv(col["wq"], col["wk"], col["wv"], rank, world))
         ok &= torch.equal(gu.weight.data, O.shard_merged([col["wg"], col["wu"]], rank, world))
+        # the paired layout (rows interleaved by the loader, no second copy) holds the same shard
+        gu2 = MergedColumnParallelLinear(128, [192, 192]).pair_rows()
+        gu2.weight.weight_loader(gu2.weight, col["wg"], 0)
+        gu2.weight.weight_loader(gu2.weight, col["wu"], 1)
+        ok &= torch.equal(gu2.reference_weight(), gu.weight.data)
+        ok &= torch.equal(gu2.paired_weight(), gu.paired_weight()) and gu2.paired_weight().data_ptr() == gu2.weight.data_ptr()
         ok &= torch.equal(row.weight.data, O.shard_row(rp["w_full"], rank, world))
         ok &= torch.equal(emb.weight.data, O.shard_column(voc["w"], rank, world))
         ok &= (qkv.tp_rank, qkv.tp_size, qkv.num_heads, qkv.num_kv_heads) == (rank, world, 8 // world, 4 // world)
