@@ -183,7 +183,7 @@ int b2_gemm_static_scratch(const void* A, int64_t lda, const void* W, int64_t ld
  *      (nanovllm/layers/layernorm.py:28-40; wired at
  *      nanovllm/models/qwen3.py:155,157,182) ---------------------------------
  * Per rank: partial = A[M,Kr] * W[N,Kr]^T (+ bias on rank 0), pushed as bf16
- * into every peer's symmetric buffer from the GEMM epilogue; then
+ * into peers' symmetric buffers from the GEMM epilogue; then
  *   s = sum_over_ranks(partial) + residual_in        (fp32)
  *   residual_out = bf16(s)
  *   normed_out   = bf16(bf16(s * rsqrt(mean(s^2) + eps)) * norm_w)
@@ -191,10 +191,47 @@ int b2_gemm_static_scratch(const void* A, int64_t lda, const void* W, int64_t ld
  * the call is the plain RowParallelLinear.forward: normed_out receives
  * bf16(sum) and residual_in/residual_out are ignored.  One launch per
  * `oneshot_tokens` rows.  Every rank must issue the same sequence of
- * collective calls (b2_rowpar_fused, b2_embed with world > 1, b2_lm_head). */
+ * collective calls (b2_rowpar_fused, b2_embed with world > 1, b2_lm_head).
+ * The library picks one of two forms per launch, with the same inputs, outputs
+ * and arithmetic (every rank ends up with all rows of both outputs):
+ *   one-shot   every rank receives every rank's partial and reduces all rows
+ *              itself: one NVLink store latency, (world-1) M N 2 bytes sent
+ *              per rank.  Used at world 2, and for more tokens than the
+ *              owner form is set to take.
+ *   row-owner  token row t is reduced by rank t mod world only: partial rows
+ *              go to their owner, which sums, adds the residual, normalises
+ *              and sends the finished row and the new residual row to every
+ *              rank: two NVLink store latencies, about
+ *              3 (world-1)/world M N 2 bytes sent per rank.  Used at world
+ *              >= 4 for up to 64 tokens (decode) unless set otherwise with
+ *              b2_ctx_set_option.  -0.0 in an output of this form is stored
+ *              as +0.0. */
 int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias,
                     int M, int N, int Kr, const void* residual_in, const void* norm_w, float eps,
                     void* normed_out, void* residual_out, void* stream);
+
+/* Forms of the fused row-parallel block, and the knobs that choose between
+ * them (no counterpart in the reference, whose only form is F.linear + NCCL).
+ * Every rank must set the same values. */
+enum {
+  B2_FORM_AUTO = 0,
+  B2_FORM_ONESHOT = 1,  /* b2_rowpar_fused, every rank reduces every row          */
+  B2_FORM_OWNER = 2,    /* b2_rowpar_fused, row t reduced by rank t mod world      */
+  B2_FORM_TWOSHOT = 3   /* b2_rowpar_fused_twoshot (different output contract)     */
+};
+enum {
+  B2_OPT_ROWPAR_FORM = 1,        /* B2_FORM_AUTO (default), _ONESHOT or _OWNER: what b2_rowpar_fused launches */
+  B2_OPT_OWNER_MAX_TOKENS = 2,   /* AUTO: largest M the row-owner form takes at world >= 4 (default 64,
+                                    at most oneshot_tokens)                                                    */
+  B2_OPT_TWOSHOT_MIN_TOKENS = 3  /* b2_rowpar_form answers B2_FORM_TWOSHOT from this M on (default 257 at
+                                    world 2, 128 above)                                                        */
+};
+int b2_ctx_set_option(b2_ctx* ctx, int option, int64_t value);
+/* Which entry point and form serve M rows of N features on this context:
+ * B2_FORM_TWOSHOT = call b2_rowpar_fused_twoshot (its output contract
+ * differs), otherwise call b2_rowpar_fused (which will run the form named).
+ * Negative on bad input.  Host arithmetic only. */
+int b2_rowpar_form(b2_ctx* ctx, int M, int N);
 
 /* The same block in its two-shot form, for many tokens (M above a few hundred)
  * at tensor-parallel size >= 2.  Token rows are dealt to the ranks in blocks
@@ -353,7 +390,8 @@ typedef struct b2_gemm_plan {
 } b2_gemm_plan;
 
 /* epilogue: 0 = b2_gemm / b2_lm_head / b2_gemm_silu_mul / b2_qkv_fused,
- * 1 = b2_rowpar_fused, 2 = b2_rowpar_fused_twoshot, 3 = b2_lm_head_sample.  resident_clusters: NULL
+ * 1 = b2_rowpar_fused (one-shot form), 2 = b2_rowpar_fused_twoshot, 3 = b2_lm_head_sample,
+ * 4 = b2_rowpar_fused (row-owner form).  resident_clusters: NULL
  * (cluster kernel not considered) or int[18]: entry [S] for 32-token tiles and
  * [9 + S] for 64-token tiles = clusters of S CTAs the device holds at once
  * (on a GPU the library asks the occupancy calculator). */
@@ -383,6 +421,10 @@ int b2_last_gemm_kernel(void);
  * number of rows of an M-row call that `rank` owns.  Negative on bad input. */
 int b2_row_owner(int token, int world, int* local_row);
 int b2_owned_rows(int M, int world, int rank);
+/* The same for the row-owner form of b2_rowpar_fused: row t belongs to rank
+ * t mod world, at row t / world of that rank's inbox. */
+int b2_owner_form_row(int token, int world, int* local_row);
+int b2_owner_form_rows(int M, int world, int rank);
 
 #ifdef __cplusplus
 }

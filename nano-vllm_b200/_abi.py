@@ -21,6 +21,8 @@ lib = C.CDLL(LIB_PATH)
 
 OK, ERR_ARG, ERR_SHAPE, ERR_CUDA, ERR_STATE, ERR_TIMEOUT, ERR_UNSUPPORTED = range(7)
 HANDLE_BYTES = 64
+FORM_AUTO, FORM_ONESHOT, FORM_OWNER, FORM_TWOSHOT = range(4)
+OPT_ROWPAR_FORM, OPT_OWNER_MAX_TOKENS, OPT_TWOSHOT_MIN_TOKENS = 1, 2, 3
 _ERR_NAMES = {1: "bad argument", 2: "shape outside what the context was created for", 3: "CUDA error",
               4: "bad state (peers not imported?)", 5: "device-side wait timed out", 6: "unsupported"}
 WAIT_NAMES = {0: "none", 1: "GEMM: TMA stage never filled", 2: "GEMM: stage never freed", 3: "GEMM: accumulator never completed",
@@ -58,6 +60,8 @@ SIGNATURES = {
     "b2_gemm_silu_mul": [_p, _p, _i64, _p, _i64, _p, _i64, _i, _i, _i, _p],
     "b2_gemm_static_scratch": [_p, _i64, _p, _i64, _p, _p, _i64, _i, _i, _i, _p],
     "b2_rowpar_fused": [_p, _p, _i64, _p, _i64, _p, _i, _i, _i, _p, _p, _f, _p, _p, _p],
+    "b2_ctx_set_option": [_p, _i, _i64],
+    "b2_rowpar_form": [_p, _i, _i],
     "b2_rowpar_fused_twoshot": [_p, _p, _i64, _p, _i64, _p, _i, _i, _i, _p, _p, _f, C.POINTER(_p), _p, _p],
     "b2_rmsnorm": [_p, _i64, _p, _f, _i, _i, _p, _i64, _p],
     "b2_add_rmsnorm": [_p, _p, _p, _f, _i, _i, _p, _p, _p],
@@ -80,6 +84,8 @@ SIGNATURES = {
     "b2_last_gemm_kernel": [],
     "b2_row_owner": [_i, _i, C.POINTER(_i)],
     "b2_owned_rows": [_i, _i, _i],
+    "b2_owner_form_row": [_i, _i, C.POINTER(_i)],
+    "b2_owner_form_rows": [_i, _i, _i],
 }
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)

@@ -359,6 +359,13 @@ struct b2_ctx {
   size_t off_rowcnt;    // two-shot: [2 parity] uint32 rows received in off_out
   size_t off_keybox;    // fused sampler, used on rank 0: [2 parity][world][max_seqs] uint64 best (score, vocab id) of every rank
   size_t off_tokens;    // [2 parity][max_seqs] int64 token inbox, -1 = not written
+  size_t off_inbox3;    // owner form: [2 parity][world][ceil(oneshot_tokens/world)][hidden] bf16 partial rows of the rows this rank owns
+  size_t off_land;      // owner form: [2 parity][2 planes: normed, residual][oneshot_tokens][hidden] bf16 finished rows, written by their owners
+
+  // which form of the fused row-parallel block b2_rowpar_fused launches (b2_ctx_set_option)
+  int rowpar_form;         // B2_FORM_AUTO / ONESHOT / OWNER
+  int owner_max_tokens;    // AUTO: the owner form serves up to this many tokens at world >= 4
+  int twoshot_min_tokens;  // b2_rowpar_form: from this many tokens on callers should use b2_rowpar_fused_twoshot
 
   // rank-local scratch
   float* splitk_ws;     // stream-K partial accumulators

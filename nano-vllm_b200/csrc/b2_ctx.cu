@@ -1,6 +1,7 @@
 // Context: symmetric buffers shared between tensor-parallel ranks through CUDA
 // IPC, rank-local scratch, the host-visible status word, and the TMA
 // descriptor encoder.
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -112,6 +113,9 @@ int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
   if (c->cfg.oneshot_tokens <= 0) c->cfg.oneshot_tokens = 1024;
   if (c->cfg.oneshot_tokens > c->cfg.max_tokens) c->cfg.oneshot_tokens = c->cfg.max_tokens;
   if (c->cfg.timeout_ms <= 0) c->cfg.timeout_ms = 5000;
+  c->rowpar_form = B2_FORM_AUTO;
+  c->owner_max_tokens = std::min(64, c->cfg.oneshot_tokens);
+  c->twoshot_min_tokens = c->cfg.world <= 2 ? 257 : 128;
   const int rc = ctx_init(c);
   if (rc != B2_OK) {
     b2_ctx_destroy(c);  // frees whatever was allocated before the failing call; the error text stays
@@ -138,7 +142,13 @@ static int ctx_init(b2_ctx* c) {
   c->off_inbox2 = off;
   const size_t rows_per_rank = ((static_cast<size_t>(c->cfg.max_tokens) + 15) / 16 + W - 1) / W * 16;  // 16-row blocks dealt round-robin
   if (W > 1) off = align_up(off + 2 * W * rows_per_rank * H * 2, 1024);
-  c->off_logits = off;
+  // owner form of the fused row-parallel block (few tokens): owners' inbox and every rank's landing buffer
+  c->off_inbox3 = off;
+  const size_t rows3 = (static_cast<size_t>(c->cfg.oneshot_tokens) + W - 1) / W;
+  off = align_up(off + 2 * W * rows3 * H * 2, 1024);
+  c->off_land = off;
+  off = align_up(off + 2 * 2 * static_cast<size_t>(c->cfg.oneshot_tokens) * H * 2, 1024);
+  c->off_logits = off;  // everything below this offset is a data-as-flag buffer (starts out holding the sentinel)
   if (c->cfg.vocab > 0 && c->cfg.max_seqs > 0) off = align_up(off + static_cast<size_t>(c->cfg.max_seqs) * c->cfg.vocab * 2, 1024);
   c->off_flags = off;
   off = align_up(off + 256, 1024);

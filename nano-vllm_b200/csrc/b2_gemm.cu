@@ -42,6 +42,14 @@
 //              arrival counter.  A launch ends when its rank has received all rows
 //              it does not own.  NVLink carries 2 (tp-1)/tp M N 2 bytes per rank,
 //              the minimum for an all-reduce.
+//   EPI_PUSH3  the row-owner form for few tokens (decode) at tensor-parallel size >= 4, where pushing a copy of
+//              the partial to every rank costs more than a second NVLink hop.  Token row t belongs to rank
+//              t mod world.  The epilogue stores each partial row only into its owner's inbox; the owner sums
+//              the partials, adds the residual, normalises, and stores the finished row AND the new residual
+//              row into every rank's landing buffer (symmetric memory, data-as-flag like the inbox); every
+//              rank then copies the rows that have landed into the caller's tensors and puts the sentinel
+//              back.  No fence, flag or counter is on the critical path: two NVLink store latencies per call
+//              and 2 (tp-1)/tp M N 2 (+ the residual's share) bytes per rank.  Same outputs as EPI_PUSH.
 //   EPI_SAMPLE the LM head fused with the sampler: no logits are stored.  Every
 //              (token, vocab entry) score - the bf16-rounded logit, divided by the
 //              row's temperature plus Gumbel noise from a counter-based generator,
@@ -67,8 +75,8 @@ constexpr int NUM_THREADS = 192;
 constexpr int MAX_ROW_VECS = 6;  // 16-byte vectors of one row per thread in the reduce phase
 constexpr uint64_t PIPE_LIMIT_NS = 1000000000ull;  // no wait inside the GEMM pipeline lasts anywhere near this
 
-enum { EPI_STORE = 0, EPI_PUSH = 1, EPI_PUSH2 = 2, EPI_SAMPLE = 3 };
-__host__ __device__ constexpr bool is_push(int epi) { return epi == EPI_PUSH || epi == EPI_PUSH2; }  // epilogues of the fused row-parallel call
+enum { EPI_STORE = 0, EPI_PUSH = 1, EPI_PUSH2 = 2, EPI_SAMPLE = 3, EPI_PUSH3 = 4 };
+__host__ __device__ constexpr bool is_push(int epi) { return epi == EPI_PUSH || epi == EPI_PUSH2 || epi == EPI_PUSH3; }  // epilogues of the fused row-parallel call
 
 struct GemmArgs {
   int tilesP, tilesQ, kblocks;
@@ -109,6 +117,9 @@ struct GemmArgs {
   // EPI_PUSH2 (inbox / parity_stride / slot_stride then describe the row-owner inbox)
   size_t out_off, rowcnt_off;  // from inbox[r]: that rank's [max_tokens][hidden] output buffer and its [2] rows-received counters
   int rows_per_rank;
+  // EPI_PUSH3 (inbox / parity_stride / slot_stride describe the owners' inbox): from inbox[r], that rank's landing buffer
+  // [2 parity][2 planes: normed, residual][tokens][N] bf16
+  size_t land_off, land_parity_stride, land_plane_stride;
   unsigned long long* trace;  // optional [CTA][8][2] (SM clock, global ns) phase stamps; null = off
   // EPI_SAMPLE (LM head fused with the sampler; feature-lane layout only, features = vocabulary entries)
   unsigned long long* sample_keys;  // [M] best (score, vocab id) per token row, zero between calls
@@ -257,6 +268,13 @@ __host__ __device__ inline int owned_rows(int M, int world, int rank) {
   return (mine - 1) * OWN_ROWS + last_rows;
 }
 
+// Row-owner form for few tokens: row t belongs to rank t mod world (balanced for any M), at inbox row t / world.
+__host__ __device__ __forceinline__ int owner3_of(int token, int world, int& local_row) {
+  local_row = token / world;
+  return token - local_row * world;
+}
+__host__ __device__ __forceinline__ int owned_rows3(int M, int world, int rank) { return (M + world - 1 - rank) / world; }
+
 // ---------------------------------------------------------------------------
 // Output of one 32-column chunk held by a warp: thread `lane` has TMEM lane
 // (row of the P tile) q*32 + lane and columns c*32 .. c*32+31 (rows of the Q
@@ -301,6 +319,12 @@ __device__ __forceinline__ void emit_feature_lanes(const GemmArgs& a, float (&v)
         } else {
           *reinterpret_cast<uint32_t*>(a.C + token * a.ldc + fbase) = w;
         }
+      } else if (EPI == EPI_PUSH3) {
+        w = b2::scrub_sentinel(w);
+        int lrow;
+        const int owner = owner3_of(token, a.world, lrow);
+        *reinterpret_cast<uint32_t*>(a.inbox[owner] + parity * a.parity_stride + a.rank * a.slot_stride +
+                                     (static_cast<size_t>(lrow) * a.N + fbase) * 2) = w;
       } else {
         w = b2::scrub_sentinel(w);
         const size_t off = parity * a.parity_stride + a.rank * a.slot_stride +
@@ -362,6 +386,11 @@ __device__ __forceinline__ void flush_rows(const GemmArgs& a, unsigned char* wbu
       } else if (EPI == EPI_PUSH2) {
         int lrow;
         const int owner = owner_of(token, a.world, lrow);
+        *reinterpret_cast<uint4*>(a.inbox[owner] + parity * a.parity_stride + a.rank * a.slot_stride +
+                                  (static_cast<size_t>(lrow) * a.N + feature) * 2) = w;
+      } else if (EPI == EPI_PUSH3) {
+        int lrow;
+        const int owner = owner3_of(token, a.world, lrow);
         *reinterpret_cast<uint4*>(a.inbox[owner] + parity * a.parity_stride + a.rank * a.slot_stride +
                                   (static_cast<size_t>(lrow) * a.N + feature) * 2) = w;
       } else {
@@ -477,12 +506,37 @@ __device__ __forceinline__ uint4 pack8f(const float (&f)[8]) {
   return make_uint4(b2::pack_bf16(f[0], f[1]), b2::pack_bf16(f[2], f[3]), b2::pack_bf16(f[4], f[5]), b2::pack_bf16(f[6], f[7]));
 }
 
-// TWO = false: every rank reduces every row (one-shot); outputs go to normed_out / residual_out.
-// TWO = true : this rank reduces only the rows it owns; a finished row goes into every rank's
-//              output buffer, the new residual stays with the owner.  Returns the rows finished.
-template <int S, bool TWO>
+// FORM_ALL   (one-shot): every rank reduces every row; outputs go to normed_out / residual_out.
+// FORM_BLOCKS(two-shot): this rank reduces only the rows it owns (16-row blocks, round-robin); a finished row
+//                        goes into every rank's output buffer, the new residual stays with the owner.
+// FORM_OWNER (few tokens): this rank reduces the rows t with t mod world == rank; the finished row and the new
+//                        residual row go into every rank's landing buffer (data-as-flag: sentinel scrubbed).
+// Returns the rows finished.
+enum { FORM_ALL = 0, FORM_BLOCKS = 1, FORM_OWNER = 2 };
+
+template <int FORM>
+__device__ __forceinline__ void store_finished(const GemmArgs& a, unsigned int parity, int plane, size_t elem_off, uint4 y) {
+  if (FORM == FORM_BLOCKS) {
+#pragma unroll
+    for (int r = 0; r < B2_MAX_WORLD; ++r)
+      if (r < a.world) *reinterpret_cast<uint4*>(a.inbox[r] + a.out_off + elem_off * 2) = y;
+  } else if (FORM == FORM_OWNER) {
+    y.x = b2::scrub_sentinel(y.x); y.y = b2::scrub_sentinel(y.y);
+    y.z = b2::scrub_sentinel(y.z); y.w = b2::scrub_sentinel(y.w);
+    const size_t off = a.land_off + parity * a.land_parity_stride + plane * a.land_plane_stride + elem_off * 2;
+#pragma unroll
+    for (int r = 0; r < B2_MAX_WORLD; ++r)
+      if (r < a.world) *reinterpret_cast<uint4*>(a.inbox[r] + off) = y;
+  } else {
+    *reinterpret_cast<uint4*>((plane == 0 ? a.normed_out : a.residual_out) + elem_off) = y;
+  }
+}
+
+template <int S, int FORM>
 __device__ __forceinline__ int reduce_rows(const GemmArgs& a, unsigned int parity, float* red, volatile int* gave_up) {
-  constexpr int G = S >= 8 ? 2 : (S == 4 ? 3 : MAX_ROW_VECS);  // vectors in flight together: G * S <= 16 loads of 16 bytes
+  // vectors in flight together: G * S loads of 16 bytes (the owner form has few rows per rank: one deeper batch per row)
+  constexpr int G = S >= 8 ? (FORM == FORM_OWNER ? 3 : 2) : (S == 4 ? 3 : MAX_ROW_VECS);
+  constexpr bool TWO = FORM == FORM_BLOCKS;
   const int nvec = a.N >> 3;
   const int tid = threadIdx.x;
   const bool with_norm = a.norm_w != nullptr;
@@ -501,13 +555,15 @@ __device__ __forceinline__ int reduce_rows(const GemmArgs& a, unsigned int parit
       if (row0 < 0) row0 = n_rows;  // a GEMM CTA: nothing to reduce
     }
   }
+  if (FORM == FORM_OWNER) n_rows = owned_rows3(a.M, a.world, a.rank);
   int rows_done = 0;
   for (int row = row0; row < n_rows; row += row_step, ++rows_done) {
     float acc[MAX_ROW_VECS][8];
     float ss = 0.f;
     const size_t row_off = static_cast<size_t>(row) * a.N;  // row inside the inbox
-    // row of the [M, N] tensors: the owned rows are the 16-row blocks rank, rank + world, ...
-    const int token = TWO ? ((((row >> OWN_SHIFT) * a.world + a.rank) << OWN_SHIFT) + (row & (OWN_ROWS - 1))) : row;
+    // row of the [M, N] tensors: two-shot owners hold the 16-row blocks rank, rank + world, ...; the owner form rows rank, rank + world, ...
+    const int token = TWO ? ((((row >> OWN_SHIFT) * a.world + a.rank) << OWN_SHIFT) + (row & (OWN_ROWS - 1)))
+                          : (FORM == FORM_OWNER ? row * a.world + a.rank : row);
     const size_t out_off = static_cast<size_t>(token) * a.N;
 #pragma unroll
     for (int g0 = 0; g0 < MAX_ROW_VECS; g0 += G) {
@@ -566,18 +622,12 @@ __device__ __forceinline__ int reduce_rows(const GemmArgs& a, unsigned int parit
           }
           if (with_norm) {
             add8(acc[g0 + i], resv[i]);
-            *reinterpret_cast<uint4*>(a.residual_out + out_off + v * 8) = pack8f(acc[g0 + i]);
+            if (FORM == FORM_OWNER) store_finished<FORM_OWNER>(a, parity, 1, out_off + v * 8, pack8f(acc[g0 + i]));
+            else *reinterpret_cast<uint4*>(a.residual_out + out_off + v * 8) = pack8f(acc[g0 + i]);
 #pragma unroll
             for (int e = 0; e < 8; ++e) ss += acc[g0 + i][e] * acc[g0 + i][e];
           } else {
-            const uint4 y = pack8f(acc[g0 + i]);
-            if (TWO) {
-#pragma unroll
-              for (int r = 0; r < B2_MAX_WORLD; ++r)
-                if (r < a.world) *reinterpret_cast<uint4*>(a.inbox[r] + a.out_off + (out_off + v * 8) * 2) = y;
-            } else {
-              *reinterpret_cast<uint4*>(a.normed_out + out_off + v * 8) = y;
-            }
+            store_finished<FORM>(a, parity, 0, out_off + v * 8, pack8f(acc[g0 + i]));
           }
         }
       }
@@ -608,18 +658,70 @@ __device__ __forceinline__ int reduce_rows(const GemmArgs& a, unsigned int parit
         o[2] = b2::bf16_round(acc[it][2] * rstd) * b2::bf16_lo(wv[it].y); o[3] = b2::bf16_round(acc[it][3] * rstd) * b2::bf16_hi(wv[it].y);
         o[4] = b2::bf16_round(acc[it][4] * rstd) * b2::bf16_lo(wv[it].z); o[5] = b2::bf16_round(acc[it][5] * rstd) * b2::bf16_hi(wv[it].z);
         o[6] = b2::bf16_round(acc[it][6] * rstd) * b2::bf16_lo(wv[it].w); o[7] = b2::bf16_round(acc[it][7] * rstd) * b2::bf16_hi(wv[it].w);
-        const uint4 y = pack8f(o);
-        if (TWO) {
-#pragma unroll
-          for (int r = 0; r < B2_MAX_WORLD; ++r)
-            if (r < a.world) *reinterpret_cast<uint4*>(a.inbox[r] + a.out_off + (out_off + v * 8) * 2) = y;
-        } else {
-          *reinterpret_cast<uint4*>(a.normed_out + out_off + v * 8) = y;
-        }
+        store_finished<FORM>(a, parity, 0, out_off + v * 8, pack8f(o));
       }
     }
   }
   return rows_done;
+}
+
+// Owner form, last phase: every (plane, row, 16-byte vector) of the landing buffer is copied into the caller's
+// tensors once it has landed (data-as-flag: the vector holds the sentinel until then) and the sentinel is put back.
+// The items are dealt to all threads of the grid, LAND_BATCH loads in flight per thread.
+constexpr int LAND_BATCH = 4;
+__device__ __forceinline__ void collect_landed_rows(const GemmArgs& a, unsigned int parity, volatile int* gave_up) {
+  const int nvec = a.N >> 3;
+  const int planes = a.norm_w != nullptr ? 2 : 1;
+  const int64_t per_plane = static_cast<int64_t>(a.M) * nvec;
+  const int64_t total = per_plane * planes;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * NUM_THREADS;
+  unsigned char* land = a.inbox[a.rank] + a.land_off + parity * a.land_parity_stride;
+  const uint4 sentinel = make_uint4(B2_SENTINEL32, B2_SENTINEL32, B2_SENTINEL32, B2_SENTINEL32);
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * NUM_THREADS + threadIdx.x; base < total; base += stride * LAND_BATCH) {
+    uint4 val[LAND_BATCH];
+    unsigned char* src[LAND_BATCH];
+    uint16_t* dst[LAND_BATCH];
+    bool todo[LAND_BATCH];
+#pragma unroll
+    for (int i = 0; i < LAND_BATCH; ++i) {
+      const int64_t idx = base + i * stride;
+      todo[i] = idx < total;
+      const int plane = (todo[i] && idx >= per_plane) ? 1 : 0;
+      const int64_t e = (todo[i] ? idx - plane * per_plane : 0) * 8;  // element offset inside the plane
+      src[i] = land + plane * a.land_plane_stride + e * 2;
+      dst[i] = (plane == 0 ? a.normed_out : a.residual_out) + e;
+    }
+    bool pending = true;
+    uint64_t t0 = 0;
+    for (uint32_t spin = 0; pending; ++spin) {
+      pending = false;
+#pragma unroll
+      for (int i = 0; i < LAND_BATCH; ++i)
+        if (todo[i]) val[i] = b2::ld_volatile_v4(src[i]);
+#pragma unroll
+      for (int i = 0; i < LAND_BATCH; ++i) {
+        if (todo[i]) {
+          if (b2::has_sentinel(val[i])) {
+            pending = true;
+          } else {
+            *reinterpret_cast<uint4*>(dst[i]) = val[i];
+            *reinterpret_cast<uint4*>(src[i]) = sentinel;
+            todo[i] = false;
+          }
+        }
+      }
+      if (pending && (spin & 0x3F) == 0x3F) {
+        if (*gave_up) return;
+        const uint64_t now = b2::globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > a.timeout_ns) {
+          *gave_up = 1;
+          b2::report_timeout(a.status, B2_WAIT_ROWS);
+          return;
+        }
+      }
+    }
+  }
 }
 
 __device__ __forceinline__ void stamp(const GemmArgs& a, int slot) {
@@ -639,17 +741,26 @@ __device__ __forceinline__ void fused_tail(const GemmArgs& a, unsigned int parit
     if (!aborted) {
       if (EPI == EPI_PUSH) {
         switch (a.world) {
-          case 1: reduce_rows<1, false>(a, parity, red, abort_flag); break;
-          case 2: reduce_rows<2, false>(a, parity, red, abort_flag); break;
-          case 4: reduce_rows<4, false>(a, parity, red, abort_flag); break;
-          default: reduce_rows<8, false>(a, parity, red, abort_flag); break;
+          case 1: reduce_rows<1, FORM_ALL>(a, parity, red, abort_flag); break;
+          case 2: reduce_rows<2, FORM_ALL>(a, parity, red, abort_flag); break;
+          case 4: reduce_rows<4, FORM_ALL>(a, parity, red, abort_flag); break;
+          default: reduce_rows<8, FORM_ALL>(a, parity, red, abort_flag); break;
         }
+      } else if (EPI == EPI_PUSH3) {
+        switch (a.world) {
+          case 1: reduce_rows<1, FORM_OWNER>(a, parity, red, abort_flag); break;  // one rank owns every row (the mechanism on a single GPU)
+          case 2: reduce_rows<2, FORM_OWNER>(a, parity, red, abort_flag); break;
+          case 4: reduce_rows<4, FORM_OWNER>(a, parity, red, abort_flag); break;
+          default: reduce_rows<8, FORM_OWNER>(a, parity, red, abort_flag); break;
+        }
+        if (threadIdx.x == 0) stamp(a, 4);  // owned rows finished and sent (overwrites "epilogue done": the GEMM part's end is stamp 5)
+        collect_landed_rows(a, parity, abort_flag);
       } else {
         int rows_done = 0;
         switch (a.world) {
-          case 2: rows_done = reduce_rows<2, true>(a, parity, red, abort_flag); break;
-          case 4: rows_done = reduce_rows<4, true>(a, parity, red, abort_flag); break;
-          default: rows_done = reduce_rows<8, true>(a, parity, red, abort_flag); break;
+          case 2: rows_done = reduce_rows<2, FORM_BLOCKS>(a, parity, red, abort_flag); break;
+          case 4: rows_done = reduce_rows<4, FORM_BLOCKS>(a, parity, red, abort_flag); break;
+          default: rows_done = reduce_rows<8, FORM_BLOCKS>(a, parity, red, abort_flag); break;
         }
         // the finished rows must be visible on every GPU before their count is
         __threadfence_system();
@@ -1230,6 +1341,13 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
         if (EPI == EPI_STORE) {
           if (a.silu_pairs) *reinterpret_cast<uint2*>(a.C + token * a.ldc + (feat >> 1)) = silu_mul_pairs(w);
           else *reinterpret_cast<uint4*>(a.C + token * a.ldc + feat) = w;
+        } else if (EPI == EPI_PUSH3) {
+          w.x = b2::scrub_sentinel(w.x); w.y = b2::scrub_sentinel(w.y);
+          w.z = b2::scrub_sentinel(w.z); w.w = b2::scrub_sentinel(w.w);
+          int lrow;
+          const int owner = owner3_of(token, a.world, lrow);
+          *reinterpret_cast<uint4*>(a.inbox[owner] + parity * a.parity_stride + a.rank * a.slot_stride +
+                                    (static_cast<size_t>(lrow) * a.N + feat) * 2) = w;
         } else {
           w.x = b2::scrub_sentinel(w.x); w.y = b2::scrub_sentinel(w.y);
           w.z = b2::scrub_sentinel(w.z); w.w = b2::scrub_sentinel(w.w);
@@ -1646,7 +1764,7 @@ template <class Resident>
 int plan_gemm(int epi, int M, int N, int K, int num_sms, int min_grid, int reducers, int64_t tile_cap, bool clusters_on,
               Resident&& resident, GemmPlan& p, int options = 0) {
   if (M <= 0 || N <= 0 || K <= 0 || num_sms <= 0) return B2_ERR_ARG;
-  p.swap = (epi != EPI_PUSH2) && M <= 256;
+  p.swap = (epi != EPI_PUSH2) && M <= (epi == EPI_PUSH3 ? 64 : 256);  // the owner form sends whole row segments: token rows above the decode sizes
   if (p.swap) p.bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   else p.bn = (N >= 256) ? 256 : (N > 64 ? 128 : 64);
   bool one_tile_per_cta = false;
@@ -1680,9 +1798,9 @@ int plan_gemm(int epi, int M, int N, int K, int num_sms, int min_grid, int reduc
     p.gemm_ctas = static_cast<int>(tiles);
     p.round_robin = 1;
   }
-  p.grid = (epi == EPI_PUSH2) ? num_sms : std::max(p.gemm_ctas, std::min(min_grid, num_sms));
+  p.grid = (epi == EPI_PUSH2 || epi == EPI_PUSH3) ? num_sms : std::max(p.gemm_ctas, std::min(min_grid, num_sms));
   p.cluster_split = 0;
-  if ((epi == EPI_STORE || epi == EPI_PUSH) && clusters_on && p.swap && p.tilesQ == 1 && p.bn <= 64) {  // up to 64 tokens: the decode sizes
+  if ((epi == EPI_STORE || epi == EPI_PUSH || epi == EPI_PUSH3) && clusters_on && p.swap && p.tilesQ == 1 && p.bn <= 64) {  // up to 64 tokens: the decode sizes
     p.cluster_split = pick_cluster_split(p.bn, p.tilesP, p.kblocks, num_sms, resident);
     if (p.cluster_split > 0) {
       p.gemm_ctas = p.tilesP * p.cluster_split;
@@ -1745,14 +1863,19 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
       return launch_pair_inst<256, EPI>(tmP, tmQh, args, args.gemm_ctas, stream);
     }
   }
-  if constexpr (EPI == EPI_STORE || EPI == EPI_PUSH) {
+  if constexpr (EPI == EPI_STORE || EPI == EPI_PUSH || EPI == EPI_PUSH3) {
     if (plan.cluster_split > 0) {
       g_last_gemm_path = 1;
       if (bn == 32) return launch_cluster_inst<32, EPI>(tmP, tmQ, args, args.tilesP, plan.cluster_split, stream);
       return launch_cluster_inst<64, EPI>(tmP, tmQ, args, args.tilesP, plan.cluster_split, stream);
     }
   }
-  if constexpr (EPI != EPI_PUSH2) {
+  if constexpr (EPI == EPI_PUSH3) {
+    if (swap) {  // at most 64 tokens in this layout
+      if (bn == 32) return launch_inst<32, true, EPI>(tmP, tmQ, args, grid, stream);
+      return launch_inst<64, true, EPI>(tmP, tmQ, args, grid, stream);
+    }
+  } else if constexpr (EPI != EPI_PUSH2) {
     if (swap) {
       switch (bn) {
         case 32: return launch_inst<32, true, EPI>(tmP, tmQ, args, grid, stream);
@@ -2084,6 +2207,39 @@ int b2_rowpar_fused_twoshot(b2_ctx* ctx, const void* A, int64_t lda, const void*
   return launch_gemm<EPI_PUSH2>(ctx, A, lda, W, ldw, M, N, Kr, args, args.rows_per_rank, static_cast<cudaStream_t>(stream));
 }
 
+// Which form of the fused row-parallel block serves M tokens on this context (B2_FORM_*).
+static int rowpar_form_for(const b2_ctx* ctx, int M, int N) {
+  const int world = ctx->cfg.world;
+  if (world >= 2 && M >= ctx->twoshot_min_tokens && N == ctx->cfg.hidden && M <= ctx->cfg.max_tokens) return B2_FORM_TWOSHOT;
+  if (ctx->rowpar_form == B2_FORM_ONESHOT || ctx->rowpar_form == B2_FORM_OWNER) return ctx->rowpar_form;
+  return (world >= 4 && M <= ctx->owner_max_tokens) ? B2_FORM_OWNER : B2_FORM_ONESHOT;
+}
+
+int b2_rowpar_form(b2_ctx* ctx, int M, int N) {
+  if (ctx == nullptr || M < 0 || N <= 0) return -B2_ERR_ARG;
+  return rowpar_form_for(ctx, M, N);
+}
+
+int b2_ctx_set_option(b2_ctx* ctx, int option, int64_t value) {
+  if (ctx == nullptr) return B2_ERR_ARG;
+  switch (option) {
+    case B2_OPT_ROWPAR_FORM:
+      if (value != B2_FORM_AUTO && value != B2_FORM_ONESHOT && value != B2_FORM_OWNER) return B2_ERR_ARG;
+      ctx->rowpar_form = static_cast<int>(value);
+      return B2_OK;
+    case B2_OPT_OWNER_MAX_TOKENS:
+      if (value < 0) return B2_ERR_ARG;
+      ctx->owner_max_tokens = static_cast<int>(std::min<int64_t>(value, ctx->cfg.oneshot_tokens));
+      return B2_OK;
+    case B2_OPT_TWOSHOT_MIN_TOKENS:
+      if (value < 1) return B2_ERR_ARG;
+      ctx->twoshot_min_tokens = static_cast<int>(std::min<int64_t>(value, 1 << 30));
+      return B2_OK;
+    default:
+      return B2_ERR_ARG;
+  }
+}
+
 int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias, int M, int N, int Kr,
                     const void* residual_in, const void* norm_w, float eps, void* normed_out, void* residual_out, void* stream) {
   if (ctx == nullptr) return B2_ERR_ARG;
@@ -2097,14 +2253,15 @@ int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int6
     return B2_ERR_ARG;
   if (bias != nullptr && !aligned16(bias)) return B2_ERR_ARG;
   const int chunk = ctx->cfg.oneshot_tokens;
+  const int world = ctx->cfg.world;
   for (int m0 = 0; m0 < M; m0 += chunk) {
     const int m = std::min(chunk, M - m0);
+    // the owner form when it is cheaper (or forced); every rank decides alike: the choice depends on M and the context only
+    int form = ctx->rowpar_form;
+    if (form == B2_FORM_AUTO) form = (world >= 4 && m <= ctx->owner_max_tokens) ? B2_FORM_OWNER : B2_FORM_ONESHOT;
     GemmArgs args{};
     args.bias = (ctx->cfg.rank == 0) ? static_cast<const uint16_t*>(bias) : nullptr;  // bias enters the sum once
-    for (int r = 0; r < ctx->cfg.world; ++r) args.inbox[r] = ctx->peer[r] + ctx->off_rowpar;
-    args.slot_stride = static_cast<size_t>(ctx->cfg.oneshot_tokens) * ctx->cfg.hidden * 2;
-    args.parity_stride = args.slot_stride * ctx->cfg.world;
-    args.world = ctx->cfg.world;
+    args.world = world;
     args.rank = ctx->cfg.rank;
     const size_t eoff = static_cast<size_t>(m0) * N;
     args.residual_in = residual_in ? static_cast<const uint16_t*>(residual_in) + eoff : nullptr;
@@ -2114,8 +2271,22 @@ int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int6
     args.residual_out = residual_out ? static_cast<uint16_t*>(residual_out) + eoff : nullptr;
     args.dstate = ctx->dstate;
     args.timeout_ns = static_cast<uint64_t>(ctx->cfg.timeout_ms) * 1000000ull;
-    rc = launch_gemm<EPI_PUSH>(ctx, static_cast<const uint16_t*>(A) + static_cast<size_t>(m0) * lda, lda, W, ldw, m, N, Kr, args, m,
-                               static_cast<cudaStream_t>(stream));
+    const uint16_t* a_rows = static_cast<const uint16_t*>(A) + static_cast<size_t>(m0) * lda;
+    if (form == B2_FORM_OWNER) {
+      const size_t rows3 = (static_cast<size_t>(ctx->cfg.oneshot_tokens) + world - 1) / world;
+      for (int r = 0; r < world; ++r) args.inbox[r] = ctx->peer[r] + ctx->off_inbox3;
+      args.slot_stride = rows3 * ctx->cfg.hidden * 2;
+      args.parity_stride = args.slot_stride * world;
+      args.land_off = ctx->off_land - ctx->off_inbox3;
+      args.land_plane_stride = static_cast<size_t>(ctx->cfg.oneshot_tokens) * ctx->cfg.hidden * 2;
+      args.land_parity_stride = 2 * args.land_plane_stride;
+      rc = launch_gemm<EPI_PUSH3>(ctx, a_rows, lda, W, ldw, m, N, Kr, args, 0, static_cast<cudaStream_t>(stream));
+    } else {
+      for (int r = 0; r < world; ++r) args.inbox[r] = ctx->peer[r] + ctx->off_rowpar;
+      args.slot_stride = static_cast<size_t>(ctx->cfg.oneshot_tokens) * ctx->cfg.hidden * 2;
+      args.parity_stride = args.slot_stride * world;
+      rc = launch_gemm<EPI_PUSH>(ctx, a_rows, lda, W, ldw, m, N, Kr, args, m, static_cast<cudaStream_t>(stream));
+    }
     if (rc != B2_OK) return rc;
   }
   return B2_OK;
@@ -2239,7 +2410,7 @@ extern "C" int b2_plan_gemm(int epilogue, int M, int N, int K, int num_sms, cons
 
 extern "C" int b2_plan_gemm_opts(int epilogue, int M, int N, int K, int num_sms, const int* resident_clusters, int options,
                                  b2_gemm_plan* plan) {
-  if (plan == nullptr || epilogue < EPI_STORE || epilogue > EPI_SAMPLE) return B2_ERR_ARG;
+  if (plan == nullptr || epilogue < EPI_STORE || epilogue > EPI_PUSH3) return B2_ERR_ARG;
   GemmPlan p{};
   const int min_grid = epilogue == EPI_PUSH ? M : 0;  // the one-shot launch also wants a CTA per token row for its reduce phase
   const int rc = plan_gemm(epilogue, M, N, K, num_sms, min_grid, 0, 1 << 20, resident_clusters != nullptr,
@@ -2312,6 +2483,16 @@ extern "C" int b2_last_gemm_kernel(void) { return g_last_gemm_path; }
 extern "C" int b2_row_owner(int token, int world, int* local_row) {
   if (token < 0 || world < 1 || local_row == nullptr) return -B2_ERR_ARG;
   return owner_of(token, world, *local_row);
+}
+
+extern "C" int b2_owner_form_row(int token, int world, int* local_row) {
+  if (token < 0 || world < 1 || local_row == nullptr) return -B2_ERR_ARG;
+  return owner3_of(token, world, *local_row);
+}
+
+extern "C" int b2_owner_form_rows(int M, int world, int rank) {
+  if (M < 0 || world < 1 || rank < 0 || rank >= world) return -B2_ERR_ARG;
+  return owned_rows3(M, world, rank);
 }
 
 extern "C" int b2_owned_rows(int M, int world, int rank) {

@@ -95,13 +95,13 @@ def gemm_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor) -> torch.Tensor:
     return out.view(*lead, I)
 
 
-def _two_shot_min_tokens(world: int) -> int:
-    """From this many tokens on the two-shot kernel is used.  One-shot pushes (world-1) copies of the partial,
-    two-shot 2 (world-1)/world: the same at world 2, 4.6x less at world 8."""
-    forced = os.environ.get("B2_TWO_SHOT_MIN_TOKENS")  # measurement switch
-    if forced:
-        return int(forced)
-    return 257 if world <= 2 else 128
+def rowpar_form(M: int, N: int) -> int:
+    """Which form of the fused row-parallel block serves M tokens of N features on this runtime
+    (_abi.FORM_ONESHOT / FORM_OWNER: b2_rowpar_fused; FORM_TWOSHOT: b2_rowpar_fused_twoshot).  The library decides."""
+    form = _lib.b2_rowpar_form(get_runtime().ctx, M, N)
+    if form < 0:
+        raise _abi.B2Error(f"b2_rowpar_form({M}, {N}): bad argument")
+    return form
 
 
 def rowpar_fused(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, residual: torch.Tensor | None,
@@ -109,9 +109,10 @@ def rowpar_fused(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, re
     """Row-parallel GEMM + all-reduce (+ residual add + RMSNorm when norm_w is given).
     Returns y, or (normed, new_residual).
 
-    For many tokens at tensor-parallel size >= 2 the two-shot kernel runs: `normed` is then a view of a
-    buffer owned by the runtime (valid until the next such call) and `new_residual` holds only the rows
-    this rank owns (16-row blocks rank, rank + world, ...); the next fused call reads exactly those rows."""
+    For many tokens at tensor-parallel size >= 2 (rowpar_form(M, N) == FORM_TWOSHOT) the two-shot kernel runs:
+    `normed` is then a view of a buffer owned by the runtime (valid until the next such call) and `new_residual`
+    holds only the rows this rank owns (16-row blocks rank, rank + world, ...); the next fused call reads exactly
+    those rows."""
     x2 = _as2d(_bf16_rows(x, "row-parallel input"))
     if x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
         x2 = x2.contiguous()
@@ -125,7 +126,7 @@ def rowpar_fused(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, re
             residual = residual.contiguous()
         res_out = torch.empty_like(residual)
     args_tail = (residual.data_ptr() if norm_w is not None else None, norm_w.data_ptr() if norm_w is not None else None, float(eps))
-    if rt.world >= 2 and M >= _two_shot_min_tokens(rt.world) and N == rt.hidden and M <= rt.max_tokens:
+    if M and rowpar_form(M, N) == _abi.FORM_TWOSHOT:
         ptr = C.c_void_p()
         _abi.check(_lib.b2_rowpar_fused_twoshot(rt.ctx, x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0),
                                                 bias.data_ptr() if bias is not None else None, M, N, Kr, *args_tail, C.byref(ptr),

@@ -53,6 +53,10 @@ class TPRuntime:
             self.poisoned = True
             raise _abi.B2Error(f"rank {self.rank}: {_abi.WAIT_NAMES.get(detail.value, detail.value)} (code {code.value})")
 
+    def set_option(self, option: int, value: int) -> None:
+        """b2_ctx_set_option (see _abi.OPT_*); every rank must set the same values."""
+        _abi.check(_abi.lib.b2_ctx_set_option(self.ctx, option, value), "b2_ctx_set_option")
+
     def reset(self, group=None) -> None:
         """Collective over the ranks: back to the state right after creation (see b2_ctx_reset).  Every rank must
         call it, with none of its kernels in flight."""

@@ -177,6 +177,44 @@ def test_rowpar_fused_single_rank(ops, rt, m, k, n):
     assert ulp_mismatch_fraction(normed, ref_n, 2) < 2e-3
 
 
+OWNER_SHAPES = [(64, 2048, 1024), (1, 4096, 4096), (8, 12288, 4096), (64, 4096, 4096), (5, 1024, 5120), (63, 512, 4096),
+                (65, 1024, 5120), (256, 8192, 5120), (300, 1024, 5120), (1024, 1024, 5120), (1500, 512, 1024)]
+
+
+@pytest.mark.parametrize("m,k,n", OWNER_SHAPES)
+def test_rowpar_owner_form_single_rank(ops, rt, m, k, n):
+    """The row-owner form of the fused block (partial rows to the owner's inbox, finished rows into the landing
+    buffer, collected into the caller's tensors), forced on one rank, where rank 0 owns every row: same outputs as
+    the one-shot form."""
+    from nanovllm_b200 import _abi
+    xs, ws, residual, norm_w = O.rowpar_case(m, k, n, 1, seed=m + k)
+    one_n, one_s = ops.rowpar_fused(xs[0].to(DEV), ws[0].to(DEV), None, residual.to(DEV), norm_w.to(DEV), 1e-6)
+    rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_OWNER)
+    try:
+        assert ops.rowpar_form(min(m, 1024), n) == _abi.FORM_OWNER
+        for i in range(3):  # consecutive launches alternate between the two inboxes / landing buffers
+            normed, new_res = ops.rowpar_fused(xs[0].to(DEV), ws[0].to(DEV), None, residual.to(DEV), norm_w.to(DEV), 1e-6)
+        y = ops.rowpar_fused(xs[0].to(DEV), ws[0].to(DEV), None, None, None, 0.0)  # plain forward through the same form
+        torch.cuda.synchronize()
+        rt.check_status()
+    finally:
+        rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_AUTO)
+    exact_n, exact_s = O.fused_row_parallel_norm_exact(xs, ws, residual, norm_w, 1e-6)
+    assert_close_bf16(new_res, exact_s, f"owner form residual {m}x{k}x{n}")
+    assert_close_bf16(normed, exact_n, f"owner form normed {m}x{k}x{n}")
+    assert_close_bf16(y, xs[0].float() @ ws[0].float().t(), f"owner form plain forward {m}x{k}x{n}")
+    if m <= 64:  # both forms run the same (deterministic) cluster GEMM: identical values
+        assert torch.equal(normed, one_n) and torch.equal(new_res, one_s)
+    # mixing the forms launch by launch keeps the two inbox parities in step
+    for i in range(4):
+        rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_OWNER if i % 2 else _abi.FORM_ONESHOT)
+        normed, new_res = ops.rowpar_fused(xs[0].to(DEV), ws[0].to(DEV), None, residual.to(DEV), norm_w.to(DEV), 1e-6)
+    rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_AUTO)
+    torch.cuda.synchronize()
+    rt.check_status()
+    assert_close_bf16(normed, exact_n, f"alternating forms {m}x{k}x{n}")
+
+
 def test_rowpar_plain_forward_and_bias(ops, rt):
     """norm_w = None is RowParallelLinear.forward: y = x W^T (+ bias)."""
     xs, ws, _, _ = O.rowpar_case(64, 1024, 1024, 1, seed=4)

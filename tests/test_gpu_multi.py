@@ -21,7 +21,7 @@ def _worker(rank: int, world: int, port: int):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     import __graft_entry__ as entry
     entry.load_package()
-    from nanovllm_b200 import ops
+    from nanovllm_b200 import ops, _abi
     from nanovllm_b200.runtime import init_runtime, shutdown_runtime
     from oracle import tp_path as O
     from tests.gpu_util import assert_close_bf16, ulp_mismatch_fraction
@@ -50,7 +50,7 @@ def _worker(rank: int, world: int, port: int):
         for (normed, new_res), xs, ws, residual, norm_w, shp in results:
             exact_n, exact_s = O.fused_row_parallel_norm_exact(xs, ws, residual, norm_w, 1e-6)
             assert_close_bf16(normed, exact_n, f"rank {rank} normed {shp}")
-            if shp[2] == rt.hidden and shp[0] >= ops._two_shot_min_tokens(world):
+            if ops.rowpar_form(shp[0], shp[2]) == _abi.FORM_TWOSHOT:
                 # two-shot form: the residual stays with the ranks that own the rows (16-row blocks, round-robin)
                 mine = (torch.arange(shp[0]) // 16) % world == rank
                 assert_close_bf16(new_res.cpu()[mine], exact_s[mine], f"rank {rank} residual (owned rows) {shp}")
@@ -66,6 +66,40 @@ def _worker(rank: int, world: int, port: int):
         gathered = [None] * world
         dist.all_gather_object(gathered, probe)
         assert all(g == gathered[0] for g in gathered), gathered
+
+        # ---- the row-owner form (row t reduced by rank t mod world, finished rows sent to everyone), forced at every size it takes ----
+        owner_shapes = [(64, 4096, 4096), (1, 2048, 1024), (8, 8192, H), (5, 1024, H), (63, 1024, 4096), (200, 1024, H), (512, 2048, 1024)] if big \
+            else [(64, 2048, 1024), (1, 1024, 1024), (8, 2048, H), (5, 1024, H), (63, 1024, 512), (200, 1024, H), (512, 1024, 1024)]
+        for i, (m, k, n) in enumerate(owner_shapes):
+            xs, ws, residual, norm_w = O.rowpar_case(m, k, n, world, seed=500 + i)
+            args = (xs[rank].to(dev), ws[rank].to(dev), None, residual.to(dev), norm_w.to(dev), 1e-6)
+            rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, 1 << 20)  # keep the many-token two-shot kernel out of this section
+            rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_ONESHOT)
+            one_n, one_s = ops.rowpar_fused(*args)
+            rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_OWNER)
+            for _ in range(3):
+                own_n, own_s = ops.rowpar_fused(*args)
+            y = ops.rowpar_fused(xs[rank].to(dev), ws[rank].to(dev), None, None, None, 0.0)
+            rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_AUTO)
+            rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, 257 if world <= 2 else 128)
+            torch.cuda.synchronize()
+            rt.check_status()
+            exact_n, exact_s = O.fused_row_parallel_norm_exact(xs, ws, residual, norm_w, 1e-6)
+            assert_close_bf16(own_n, exact_n, f"rank {rank} owner form normed {(m, k, n)}")
+            assert_close_bf16(own_s, exact_s, f"rank {rank} owner form residual {(m, k, n)}")
+            assert_close_bf16(y, sum(x.float() @ w.float().t() for x, w in zip(xs, ws)), f"rank {rank} owner form plain forward {(m, k, n)}")
+            if m <= 64:  # same partials (cluster kernel), same summation order: the two forms agree exactly
+                assert torch.equal(own_n, one_n) and torch.equal(own_s, one_s), f"rank {rank}: owner and one-shot forms differ {(m, k, n)}"
+        # forms alternating launch by launch, many times: the inbox parities stay in step on every rank
+        xs, ws, residual, norm_w = O.rowpar_case(64, 1024, 1024, world, seed=12)
+        args = (xs[rank].to(dev), ws[rank].to(dev), None, residual.to(dev), norm_w.to(dev), 1e-6)
+        for i in range(61):
+            rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_OWNER if i % 3 else _abi.FORM_ONESHOT)
+            normed, new_res = ops.rowpar_fused(*args)
+        rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_AUTO)
+        torch.cuda.synchronize()
+        rt.check_status()
+        assert_close_bf16(normed, O.fused_row_parallel_norm_exact(xs, ws, residual, norm_w, 1e-6)[0], "61 launches of alternating forms")
 
         # ---- two-shot form (many tokens): normed rows everywhere, the residual only on the rows a rank owns ----
         for i, (m, k) in enumerate([(1024, 2048), (300, 1024), (4096, 1024), (777, 2048)] if big else [(512, 1024), (300, 1024), (1040, 1024)]):

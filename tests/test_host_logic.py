@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 # ---- the GEMM launch planner (the library's own arithmetic, read through b2_plan_gemm) ----
-EPI_STORE, EPI_PUSH, EPI_PUSH2, EPI_SAMPLE = 0, 1, 2, 3
+EPI_STORE, EPI_PUSH, EPI_PUSH2, EPI_SAMPLE, EPI_PUSH3 = 0, 1, 2, 3, 4
 SMS = 148
 # clusters of S CTAs resident at once, per tile width: [S] for 32-token tiles, [9 + S] for 64-token tiles.  On a GPU
 # the library asks the occupancy calculator; these stand for a 148-SM part whose clusters of 3, 5, 6 and 7 pack badly
@@ -101,6 +101,8 @@ PLAN_SHAPES = [
     (EPI_PUSH, 64, 4096, 4096), (EPI_PUSH, 64, 5120, 1024), (EPI_PUSH, 64, 5120, 3200), (EPI_PUSH, 256, 5120, 1024), (EPI_PUSH, 1, 1024, 384),
     (EPI_PUSH2, 128, 5120, 1024), (EPI_PUSH2, 1024, 5120, 3200), (EPI_PUSH2, 8192, 5120, 1024), (EPI_PUSH2, 16384, 4096, 2048),
     (EPI_PUSH2, 300, 1024, 1536),
+    (EPI_PUSH3, 64, 4096, 512), (EPI_PUSH3, 64, 4096, 1536), (EPI_PUSH3, 1, 5120, 1024), (EPI_PUSH3, 8, 5120, 3200), (EPI_PUSH3, 64, 5120, 3200),
+    (EPI_PUSH3, 65, 5120, 1024), (EPI_PUSH3, 256, 5120, 1024), (EPI_PUSH3, 1024, 5120, 3200), (EPI_PUSH3, 200, 1024, 384),
     (EPI_SAMPLE, 64, 151936, 4096), (EPI_SAMPLE, 64, 18992, 4096), (EPI_SAMPLE, 256, 4096, 1024), (EPI_SAMPLE, 3, 512, 128),
 ]
 
@@ -110,9 +112,11 @@ def test_planner_covers_every_unit_once(pkg, epi, m, n, k):
     from nanovllm_b200 import _abi
     rc, plan = plan_gemm(_abi, epi, m, n, k)
     assert rc == 0
-    assert plan.swap == (1 if (epi != EPI_PUSH2 and m <= 256) else 0)
+    assert plan.swap == (1 if (epi != EPI_PUSH2 and m <= (64 if epi == EPI_PUSH3 else 256)) else 0)
     if epi == EPI_PUSH2:
         assert plan.grid == SMS and plan.cluster_split == 0
+    if epi == EPI_PUSH3:   # decode sizes run in the cluster kernel (its CTAs also reduce and collect); above, stream-K on all SMs
+        assert (plan.cluster_split > 0 and plan.grid == plan.gemm_ctas) if m <= 64 else (plan.cluster_split == 0 and plan.grid == SMS)
     if epi == EPI_SAMPLE:
         assert plan.cluster_split == 0 and plan.tiles_q == 1      # the fused sampler runs in the stream-K kernel, one token tile
     check_plan(_abi, plan, m, n, k)
@@ -139,7 +143,9 @@ def test_planner_choices_for_the_decode_shapes(pkg):
     assert (p.cluster_split, p.gemm_ctas, p.grid) == (0, 1, 128)  # the launch keeps a CTA per token row for the reduce phase
     rc, p = plan_gemm(_abi, EPI_PUSH, 64, 5120, 1024)             # one-shot at decode size: the cluster kernel reduces too
     assert (p.tiles_p, p.cluster_split, p.grid) == (40, 3, 120)
-    for bad in [(0, 0, 64, 64), (0, 64, 0, 64), (0, 64, 64, 0), (4, 64, 64, 64), (-1, 64, 64, 64)]:
+    rc, p = plan_gemm(_abi, EPI_PUSH3, 64, 4096, 512)             # row-owner form, o_proj of Qwen3-8B at 8 ranks: 32 tiles x split 4
+    assert (p.tiles_p, p.cluster_split, p.grid) == (32, 4, 128)
+    for bad in [(0, 0, 64, 64), (0, 64, 0, 64), (0, 64, 64, 0), (5, 64, 64, 64), (-1, 64, 64, 64)]:
         assert plan_gemm(_abi, *bad)[0] == 1                      # B2_ERR_ARG
     assert _abi.lib.b2_plan_gemm(0, 64, 64, 64, SMS, None, None) == 1
 
@@ -166,7 +172,7 @@ def test_whole_tile_option(pkg, epi, m, n, k):
 
 
 @settings(max_examples=120, deadline=None)
-@given(epi=st.sampled_from([EPI_STORE, EPI_PUSH, EPI_PUSH2, EPI_SAMPLE]), m=st.integers(1, 3000), n8=st.integers(1, 1200), k8=st.integers(1, 700),
+@given(epi=st.sampled_from([EPI_STORE, EPI_PUSH, EPI_PUSH2, EPI_SAMPLE, EPI_PUSH3]), m=st.integers(1, 3000), n8=st.integers(1, 1200), k8=st.integers(1, 700),
        sms=st.sampled_from([148, 132, 7, 1]))
 def test_planner_property(epi, m, n8, k8, sms):
     import __graft_entry__
@@ -286,6 +292,27 @@ def test_two_shot_row_ownership(pkg, m, world):
     max_rows = ((16384 + 15) // 16 + world - 1) // world * 16
     assert max(lib.b2_owned_rows(min(m, 16384), world, r) for r in range(world)) <= max_rows
     assert lib.b2_owned_rows(m, world, world) < 0 and lib.b2_row_owner(-1, world, C.byref(C.c_int())) < 0
+
+
+# ---- row-owner form for few tokens: row t belongs to rank t mod world ----
+@pytest.mark.parametrize("m", [1, 3, 7, 8, 9, 63, 64, 65, 200, 1024])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_owner_form_row_ownership(pkg, m, world):
+    from nanovllm_b200 import _abi
+    lib = _abi.lib
+    per_rank = {r: [] for r in range(world)}
+    for t in range(m):
+        local = C.c_int()
+        o = lib.b2_owner_form_row(t, world, C.byref(local))
+        assert (o, local.value) == (t % world, t // world)
+        per_rank[o].append(local.value)
+    for r in range(world):
+        n = lib.b2_owner_form_rows(m, world, r)
+        assert per_rank[r] == list(range(n))          # dense local rows: the reduce phase walks 0 .. n-1, token = row * world + rank
+        assert all(row * world + r < m for row in range(n))
+        assert n <= (1024 + world - 1) // world         # the inbox holds ceil(oneshot_tokens / world) rows per source
+    assert sum(lib.b2_owner_form_rows(m, world, r) for r in range(world)) == m
+    assert lib.b2_owner_form_rows(m, world, world) < 0 and lib.b2_owner_form_row(-1, world, C.byref(C.c_int())) < 0
 
 
 # ---- cluster kernel: 4-column groups of the accumulator dealt round-robin to the S CTAs of a cluster ----
