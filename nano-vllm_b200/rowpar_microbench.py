@@ -1,18 +1,23 @@
 """Microbenchmark of the fused row-parallel block (GEMM + cross-GPU reduction +
-residual add + RMSNorm in one launch) next to the reference's formulation of
-the same block on the same GPUs: F.linear, NCCL all_reduce
-(nanovllm/layers/linear.py:153-155) and the torch.compile'd add + RMSNorm
-(nanovllm/layers/layernorm.py:28-40).
+residual add + RMSNorm in one launch) next to the reference's own modules for
+the same block on the same GPUs: RowParallelLinear (F.linear + NCCL
+all_reduce, nanovllm/layers/linear.py:131-156) followed by RMSNorm's
+add_rms_forward (torch.compile'd, nanovllm/layers/layernorm.py:28-40),
+imported from the reference's install under baseline/_ref when it is there
+(a restatement of the same calls otherwise; the JSON says which).
 
 Both sides run inside CUDA graphs, as the decode path does, over a rotation of
 weight copies larger than L2, and are timed with CUDA events (max over ranks).
+After the timing one more call of each side runs on the same tensors and the
+outputs are compared: ours against an fp32 statement of the block (per element,
+|err| <= 2e-2 + 1e-2 |ref|) and against the reference modules' bf16 result.
 
 Stand-alone, under torchrun with N ranks, it runs the Qwen3-32B shapes
 (hidden 5120; o_proj K = 8192, down_proj K = 25600, split over N) for
 M in {1, 8, 64, 256, 1024, 8192} and prints one JSON row per case:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        nano-vllm_b200/rowpar_microbench.py [--tokens 1,8,64] [--no-nccl]
+        nano-vllm_b200/rowpar_microbench.py [--tokens 1,8,64] [--no-nccl] [--forms]
 """
 from __future__ import annotations
 
@@ -24,7 +29,11 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool (nominal 900)
+# Peer-copy bandwidth per direction per GPU through NVSwitch used as the NVLink term of the roofline (nominal
+# 900 GB/s); the stand-alone run measures the copy itself and prints it beside every row.
+NVLINK_GBS = 770.0
+NVLINK_NOMINAL_GBS = 900.0
+TOL_ABS, TOL_REL = 2e-2, 1e-2
 
 
 def roofline_us(m: int, n: int, kr: int, world: int, peaks: dict) -> dict:
@@ -32,9 +41,10 @@ def roofline_us(m: int, n: int, kr: int, world: int, peaks: dict) -> dict:
     nvl = 2.0 * (world - 1) / world * m * n * 2
     hbm = 2.0 * (m * kr + n * kr + 3 * m * n + n)
     t = {"flops_us": flops / (peaks["bf16_tflops"] * 1e12) * 1e6, "nvlink_us": nvl / (NVLINK_GBS * 1e9) * 1e6,
-         "hbm_us": hbm / (peaks["hbm_gbs"] * 1e9) * 1e6}
+         "hbm_us": hbm / (peaks["hbm_gbs"] * 1e9) * 1e6, "nvlink_bytes": nvl}
     t["roof_us"] = max(t["flops_us"], t["nvlink_us"], t["hbm_us"])
     t["roof2_us"] = max(t["flops_us"], t["nvlink_us"])  # "the slower of compute at peak and bytes over NVLink"
+    t["roof_us_nominal_nvlink"] = max(t["flops_us"], nvl / (NVLINK_NOMINAL_GBS * 1e9) * 1e6, t["hbm_us"])
     return t
 
 
@@ -70,7 +80,7 @@ def time_in_graph(make_call, n_variants: int, iters: int) -> float:
     return _max_over_ranks(e0.elapsed_time(e1) * 1e3 / (replays * n_variants))
 
 
-def _reference_add_rms(x, residual, weight, eps):
+def _restated_add_rms(x, residual, weight, eps):
     orig = x.dtype
     x = x.float().add_(residual.float())
     residual = x.to(orig)
@@ -79,37 +89,124 @@ def _reference_add_rms(x, residual, weight, eps):
     return x.to(orig).mul_(weight), residual
 
 
-def compare_blocks(blocks, peaks: dict, iters: int = 200, with_nccl: bool = True) -> dict:
-    from . import ops
+def reference_install() -> str | None:
+    """Directory of the reference's install (baseline/_ref beside the package), or None."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    path = os.path.join(os.path.dirname(here), "baseline", "_ref")
+    return path if os.path.isdir(os.path.join(path, "nanovllm")) else None
+
+
+class ReferenceBlock:
+    """The reference's formulation of the block on this rank's GPU: its own RowParallelLinear and RMSNorm modules
+    when the install is present (`kind` = "reference modules"), the same calls restated otherwise."""
+
+    def __init__(self, n: int, k_total: int, kr: int, norm_w: torch.Tensor, eps: float, dev):
+        self.kind = "restated calls (F.linear + dist.all_reduce + torch.compile'd add-RMSNorm)"
+        self.linear = self.norm = None
+        self.norm_w, self.eps = norm_w, eps
+        path = reference_install()
+        if path is not None and dist.is_initialized():
+            try:
+                if path not in sys.path:
+                    sys.path.insert(0, path)
+                from nanovllm.layers.layernorm import RMSNorm
+                from nanovllm.layers.linear import RowParallelLinear
+                prev = torch.get_default_dtype()
+                torch.set_default_dtype(torch.bfloat16)
+                try:
+                    with torch.device(dev):
+                        self.linear = RowParallelLinear(k_total, n, bias=False)
+                        self.norm = RMSNorm(n, eps=eps)
+                finally:
+                    torch.set_default_dtype(prev)
+                assert tuple(self.linear.weight.shape) == (n, kr)
+                self.norm.weight.data.copy_(norm_w)
+                self.kind = "reference modules (nanovllm RowParallelLinear + RMSNorm, NCCL all_reduce)"
+            except Exception as ex:  # fall back to the restated calls, and say why
+                self.linear = self.norm = None
+                self.kind += f" [reference import failed: {ex!r}]"[:200]
+        if self.linear is None:
+            try:
+                self._add_rms = torch.compile(_restated_add_rms)
+            except Exception:
+                self._add_rms = _restated_add_rms
+
+    def __call__(self, x, w, residual):
+        if self.linear is not None:
+            self.linear.weight.data = w
+            return self.norm(self.linear(x), residual)
+        y = F.linear(x, w)
+        if dist.get_world_size() > 1:
+            dist.all_reduce(y)
+        return self._add_rms(y, residual, self.norm_w, self.eps)
+
+
+def _error_stats(got: torch.Tensor, ref: torch.Tensor) -> dict:
+    got, ref = got.float(), ref.float()
+    err = (got - ref).abs()
+    big = ref.abs() >= 1.0
+    return {"max_abs_err": err.max().item(), "max_rel_err": (err[big] / ref.abs()[big]).max().item() if bool(big.any()) else 0.0,
+            "within_tolerance": bool((err <= TOL_ABS + TOL_REL * ref.abs()).all())}
+
+
+def compare_blocks(blocks, peaks: dict, iters: int = 200, with_nccl: bool = True, forms: bool = False) -> dict:
+    """blocks: (name, M, N, Kr) per case.  Returns per case the timings, the roofline and the parity of the last call.
+    forms=True also times b2_rowpar_fused with each of its two forms forced (one-shot, row-owner)."""
+    from . import _abi, ops
+    from .runtime import get_runtime
+    rt = get_runtime()
     world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
     dev = torch.device("cuda", torch.cuda.current_device())
     out = {}
-    norm_fn = _reference_add_rms
-    if with_nccl:
-        try:
-            norm_fn = torch.compile(_reference_add_rms)
-        except Exception:
-            norm_fn = _reference_add_rms
     for name, m, n, kr in blocks:
         n_w = int(max(2, min(64, (300 << 20) // (n * kr * 2) + 1)))
-        ws = [(torch.randn(n, kr, device=dev) * 0.02).bfloat16() for _ in range(n_w)]
-        x = torch.randn(m, kr, device=dev).bfloat16()
-        residual = torch.randn(m, n, device=dev).bfloat16()
-        norm_w = (torch.rand(n, device=dev) + 0.5).bfloat16()
-        ours = time_in_graph(lambda i: ops.rowpar_fused(x, ws[i % n_w], None, residual, norm_w, 1e-6), n_w, iters)
-        row = {"M": m, "N": n, "Kr": kr, "tp": world, "b200_us": ours}
+        g_own = torch.Generator(device=dev).manual_seed(1000 + 17 * rank + m + kr)   # this rank's shard of the operands
+        g_all = torch.Generator(device=dev).manual_seed(77 + m + n)                  # what every rank holds alike
+        ws = [(torch.randn(n, kr, device=dev, generator=g_own) * 0.02).bfloat16() for _ in range(n_w)]
+        x = torch.randn(m, kr, device=dev, generator=g_own).bfloat16()
+        residual = torch.randn(m, n, device=dev, generator=g_all).bfloat16()
+        norm_w = (torch.rand(n, device=dev, generator=g_all) + 0.5).bfloat16()
+
+        def ours_call(i):
+            return ops.rowpar_fused(x, ws[i % n_w], None, residual, norm_w, 1e-6)
+
+        form = ops.rowpar_form(m, n)
+        ours = time_in_graph(ours_call, n_w, iters)
+        row = {"M": m, "N": n, "Kr": kr, "tp": world, "b200_us": ours,
+               "form": {_abi.FORM_ONESHOT: "one-shot", _abi.FORM_OWNER: "row-owner", _abi.FORM_TWOSHOT: "two-shot"}[form]}
+        if forms and world > 1 and m <= rt.oneshot_tokens:
+            rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, 1 << 30)
+            for f, label in ((_abi.FORM_ONESHOT, "oneshot_us"), (_abi.FORM_OWNER, "owner_us")):
+                rt.set_option(_abi.OPT_ROWPAR_FORM, f)
+                row[label] = time_in_graph(ours_call, n_w, iters)
+            rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_AUTO)
+            rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, 257 if world <= 2 else 128)
         row.update(roofline_us(m, n, kr, world, peaks))
         row["frac_of_roof"] = row["roof_us"] / ours
+        row["nvlink_egress_gbs"] = row["nvlink_bytes"] / (ours * 1e-6) / 1e9 if world > 1 else 0.0
+        # ---- parity of one more call on the first weight copy ----
+        normed, new_res = ours_call(0)
+        normed = normed.clone()
+        y32 = x.float() @ ws[0].float().t()
+        if world > 1:
+            dist.all_reduce(y32)  # fp32 sum over the ranks: the exact block
+        s = y32 + residual.float()
+        exact = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * norm_w.float()
+        row["parity_vs_fp32"] = _error_stats(normed, exact)
+        if form != _abi.FORM_TWOSHOT:  # (the two-shot form keeps the residual row-sharded)
+            row["parity_vs_fp32"]["residual_within_tolerance"] = _error_stats(new_res, s)["within_tolerance"]
         if with_nccl and world > 1:
-            def ref_call(i):
-                y = F.linear(x, ws[i % n_w])
-                dist.all_reduce(y)
-                return norm_fn(y, residual, norm_w, 1e-6)
             try:
-                row["nccl_us"] = time_in_graph(ref_call, n_w, iters)
+                ref = ReferenceBlock(n, kr * world, kr, norm_w, 1e-6, dev)
+                row["reference_kind"] = ref.kind
+                row["nccl_us"] = time_in_graph(lambda i: ref(x, ws[i % n_w], residual), n_w, iters)
                 row["speedup_vs_nccl"] = row["nccl_us"] / ours
+                ref_n, _ = ref(x.clone(), ws[0], residual.clone())
+                row["parity_vs_reference"] = {"max_abs_diff": (normed.float() - ref_n.float()).abs().max().item(),
+                                              "reference_vs_fp32": _error_stats(ref_n, exact)}
             except Exception as ex:
-                row["nccl_error"] = repr(ex)[:160]
+                row["nccl_error"] = repr(ex)[:200]
         out[name] = row
         del ws
         torch.cuda.empty_cache()
@@ -127,7 +224,6 @@ def compare_model_forward(runner, bs: int, iters: int = 20) -> dict:
                   flash-attn decode call (nanovllm/layers/attention.py:72-74).
     Returns microseconds per pass (max over ranks)."""
     from flash_attn import flash_attn_with_kvcache
-    from .utils.context import set_context, reset_context
     world = dist.get_world_size() if dist.is_initialized() else 1
     model = runner.model.model
     gv = runner.graph_vars
@@ -152,9 +248,9 @@ def compare_model_forward(runner, bs: int, iters: int = 20) -> dict:
         return F.silu(x[..., 0::2]) * x[..., 1::2]
 
     try:
-        rms, add_rms, rope, silu_mul = (torch.compile(f) for f in (_rms, lambda x, r, w: _reference_add_rms(x, r, w, eps), _rope, _silu_mul))
+        rms, add_rms, rope, silu_mul = (torch.compile(f) for f in (_rms, lambda x, r, w: _restated_add_rms(x, r, w, eps), _rope, _silu_mul))
     except Exception:
-        rms, add_rms, rope, silu_mul = _rms, (lambda x, r, w: _reference_add_rms(x, r, w, eps)), _rope, _silu_mul
+        rms, add_rms, rope, silu_mul = _rms, (lambda x, r, w: _restated_add_rms(x, r, w, eps)), _rope, _silu_mul
 
     @torch.inference_mode()
     def reference_pass():
@@ -221,43 +317,29 @@ def compare_model_forward(runner, bs: int, iters: int = 20) -> dict:
             "what": "model forward only (embedding, all decoder layers, final norm); LM head and sampling excluded on both sides"}
 
 
-TRACE_PHASES = ["set-up done", "first operand tile landed", "last MMA issued", "earlier kernels complete", "epilogue done",
-                "GEMM part left", "reduce phase done", "kernel entry"]
-
-
-def trace_phases(make_call, warmup: int = 3) -> dict:
-    """Phase stamps of one launch of the fused block on this rank (the library's b2_trace): for every phase the
-    minimum, median and maximum over the CTAs, in microseconds after the first CTA entered the kernel.  Each GPU
-    has its own clock, so only the differences inside one rank mean something."""
-    import ctypes as C
-
-    import numpy as np
-
-    from . import _abi
-    from .runtime import get_runtime
-    rt = get_runtime()
-    for i in range(warmup):
-        make_call(i)
-    torch.cuda.synchronize()
-    _abi.check(_abi.lib.b2_trace(rt.ctx, 1, None, 0), "b2_trace on")
-    make_call(warmup)
-    torch.cuda.synchronize()
-    max_ctas = 256
-    buf = (C.c_ulonglong * (max_ctas * 16))()
-    _abi.check(_abi.lib.b2_trace(rt.ctx, 0, buf, max_ctas), "b2_trace read")
-    ns = np.frombuffer(buf, dtype=np.uint64).reshape(max_ctas, 8, 2)[:, :, 1].astype(np.int64)
-    live = ns[:, 7] > 0
-    out = {"ctas": int(live.sum())}
-    if not live.any():
-        return out
-    t0 = ns[live, 7].min()
-    for i in (7, 0, 3, 1, 2, 4, 5, 6):
-        v = ns[live, i]
-        v = v[v > 0]
-        if len(v):
-            r = (v - t0) / 1e3
-            out[TRACE_PHASES[i]] = [round(float(r.min()), 2), round(float(np.median(r)), 2), round(float(r.max()), 2)]
-    return out
+def measure_peer_copy_gbs(local: int, world: int, mib: int = 512) -> float | None:
+    """GB/s of a device-to-device copy from this rank's GPU to the next rank's, every rank copying at once
+    (one direction of every GPU's NVLink ports busy): the figure the NVLink term of the roofline stands for."""
+    if world < 2:
+        return None
+    try:
+        src = torch.empty(mib << 20, dtype=torch.uint8, device=torch.device("cuda", local))
+        dst = torch.empty(mib << 20, dtype=torch.uint8, device=torch.device("cuda", (local + 1) % world))
+        for _ in range(2):
+            dst.copy_(src, non_blocking=True)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(8):
+            dst.copy_(src, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = _max_over_ranks(e0.elapsed_time(e1) / 8)
+        del src, dst
+        return (mib << 20) / (ms * 1e-3) / 1e9
+    except Exception:
+        return None
 
 
 def main():
@@ -272,8 +354,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", default="1,8,64,256,1024,8192")
     ap.add_argument("--no-nccl", action="store_true")
+    ap.add_argument("--forms", action="store_true", help="also time b2_rowpar_fused with each of its forms forced")
     ap.add_argument("--iters", type=int, default=200)
-    ap.add_argument("--trace", action="store_true", help="instead of timing, print every rank's per-phase stamps of one launch per shape")
+    ap.add_argument("--shapes", default="32b", choices=["32b", "8b"], help="Qwen3-32B (hidden 5120) or Qwen3-8B (hidden 4096) projections")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
@@ -286,29 +369,16 @@ def main():
     if os.path.exists(p):
         peaks = json.load(open(p))
     ms = [int(v) for v in a.tokens.split(",")]
-    init_runtime(max_tokens=max(ms), hidden=5120, oneshot_tokens=1024)
+    hidden, projections = (5120, (("o_proj", 8192), ("down_proj", 25600))) if a.shapes == "32b" else (4096, (("o_proj", 4096), ("down_proj", 12288)))
+    peer_gbs = mb.measure_peer_copy_gbs(local, world)
+    init_runtime(max_tokens=max(ms), hidden=hidden, oneshot_tokens=1024)
     try:
-        for proj, k_total in (("o_proj", 8192), ("down_proj", 25600)):
+        for proj, k_total in projections:
             for m in ms:
-                if a.trace:
-                    from nanovllm_b200 import ops
-                    kr = k_total // world
-                    dev = torch.device("cuda", local)
-                    ws = [(torch.randn(5120, kr, device=dev) * 0.02).bfloat16() for _ in range(4)]
-                    x = torch.randn(m, kr, device=dev).bfloat16()
-                    residual = torch.randn(m, 5120, device=dev).bfloat16()
-                    norm_w = (torch.rand(5120, device=dev) + 0.5).bfloat16()
-                    dist.barrier()
-                    stamps = mb.trace_phases(lambda i: ops.rowpar_fused(x, ws[i % 4], None, residual, norm_w, 1e-6))
-                    everyone = [None] * world
-                    dist.all_gather_object(everyone, stamps)
-                    if rank == 0:
-                        for r, st in enumerate(everyone):
-                            print(json.dumps({"proj": proj, "M": m, "Kr": kr, "tp": world, "rank": r} | st), flush=True)
-                    continue
-                res = mb.compare_blocks([(proj, m, 5120, k_total // world)], peaks, iters=a.iters if m <= 1024 else 20, with_nccl=not a.no_nccl)
+                res = mb.compare_blocks([(proj, m, hidden, k_total // world)], peaks, iters=a.iters if m <= 1024 else 20, with_nccl=not a.no_nccl,
+                                        forms=a.forms)
                 if rank == 0:
-                    print(json.dumps(res[proj] | {"proj": proj}), flush=True)
+                    print(json.dumps(res[proj] | {"proj": proj, "peer_copy_gbs_measured": peer_gbs}), flush=True)
     finally:
         shutdown_runtime()
         dist.destroy_process_group()

@@ -23,6 +23,7 @@ class TPRuntime:
             raise RuntimeError("nanovllm_b200 needs a CUDA device (B200, sm_100a); there is no CPU path")
         self.rank, self.world, self.device = rank, world, device
         self.vocab, self.max_seqs, self.hidden, self.max_tokens = vocab, max_seqs, hidden, max_tokens
+        self.oneshot_tokens = min(oneshot_tokens if oneshot_tokens > 0 else 1024, max_tokens)
         cfg = _abi.Config(rank, world, device, max_tokens, hidden, oneshot_tokens, vocab, max_seqs, timeout_ms)
         ctx = C.c_void_p()
         torch.cuda.set_device(device)
