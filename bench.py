@@ -143,6 +143,32 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def reference_engine_gpu(tp: int, steps: int, warmup: int, timeout_s: float = 600.0) -> dict:
+    """The unmodified reference engine (NCCL, flash-attn, CUDA graphs) on the same GPUs and workload, in a process
+    group of its own (baseline/reference_engine.py); returns its JSON line, or why there is none."""
+    import signal
+    script = os.path.join(ROOT, "baseline", "reference_engine.py")
+    cmd = [sys.executable, script, "--tp", str(tp), "--workload", "decode8b", "--steps", str(steps), "--warmup", str(warmup),
+           "--batch", str(BATCH), "--prompt-len", str(PROMPT_LEN)]
+    env = {k: v for k, v in os.environ.items() if not (k.startswith("TORCHELASTIC_") or k in (
+        "RANK", "WORLD_SIZE", "LOCAL_RANK", "LOCAL_WORLD_SIZE", "GROUP_RANK", "GROUP_WORLD_SIZE", "ROLE_RANK", "ROLE_WORLD_SIZE", "ROLE_NAME",
+        "MASTER_ADDR", "MASTER_PORT", "OMP_NUM_THREADS"))}
+    try:
+        proc = subprocess.Popen(cmd, cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, start_new_session=True)
+        try:
+            out, err = proc.communicate(timeout=timeout_s)
+        except subprocess.TimeoutExpired:
+            os.killpg(proc.pid, signal.SIGKILL)  # the engine's own process group: rank 0 and the ranks it spawned
+            proc.communicate()
+            return {"unavailable": f"the reference engine did not finish within {timeout_s:.0f} s"}
+        lines = [l for l in out.splitlines() if l.startswith("{")]
+        if proc.returncode != 0 or not lines:
+            return {"unavailable": f"the reference engine exited with code {proc.returncode}: {(err or out)[-300:]}"}
+        return json.loads(lines[-1])
+    except Exception as ex:
+        return {"unavailable": repr(ex)[:300]}
+
+
 def run_b200(args) -> None:
     import torch
     import torch.distributed as dist
@@ -266,7 +292,7 @@ def run_b200(args) -> None:
 
     # ---- the whole model forward next to the reference's formulation of it (cuBLAS + NCCL + compiled elementwise) ----
     forward_cmp = None
-    if not args.skip_nccl:
+    if args.forward_compare:
         try:
             from nanovllm_b200 import rowpar_microbench as mb
             resident.load(fresh_seqs())
@@ -279,18 +305,57 @@ def run_b200(args) -> None:
         ref = cpu_reference(1, 1, 64, max_seconds=15.0)
         cpu = {k: ref[k] for k in ("value", "unit", "cores", "kind", "sample")}
 
+    # ---- parity of what was timed: the device-resident loop and step() must pick the same tokens ----
+    resident.load(fresh_seqs())
+    from_resident = []
+    for _ in range(8):
+        resident.replay()
+        from_resident.append(resident.tokens.tolist())
+    seqs = fresh_seqs()
+    same = total = 0
+    for k in range(8):
+        toks = runner.step(seqs, False)
+        for s_, t in zip(seqs, toks):
+            s_.token_ids.append(t)
+        same += sum(int(a == b) for a, b in zip(from_resident[k], toks))
+        total += len(toks)
+    runner.runtime.check_status()
+    parity = {"resident_loop_vs_step_tokens_identical": f"{same}/{total}",
+              "note": "greedy tokens of 8 decode steps of the 64 sequences through both timed paths; tests/test_gpu_decode_paths.py checks both against the oracle"}
+    if block_cmp is not None and "error" not in block_cmp:
+        parity["rowpar_block_within_bf16_tolerance_of_fp32"] = all(r.get("parity_vs_fp32", {}).get("within_tolerance", False) for r in block_cmp.values())
+
+    clock_summary = clocks.summary()
+    runner.exit()
+    del resident, runner, layers, paired
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+
+    # ---- the unmodified reference engine (its NCCL build) on the same GPUs, after this arm has released them ----
+    ref_gpu = None
+    if not args.skip_reference_gpu:
+        barrier()
+        if rank == 0:
+            ref_gpu = reference_engine_gpu(world, min(K, 64), 8)
+        if world > 1:
+            dist.barrier()
+
     if rank == 0:
         line = {"metric": METRIC, "value": BATCH * K / (total_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
                 "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": workload(world), "clocks": clocks.summary(),
+                "config": workload(world), "clocks": clock_summary,
                 "e2e": {"value": BATCH * K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / K},
-                "gpu_launches": launches, "roofline": roofline, "step_roofline": step_roof, "cpu_baseline": cpu}
+                "gpu_launches": launches, "roofline": roofline, "step_roofline": step_roof, "cpu_baseline": cpu, "parity": parity}
         if block_cmp is not None:
             line["rowpar_block_us"] = block_cmp
         if forward_cmp is not None:
             line["model_forward_us"] = forward_cmp
+        if ref_gpu is not None:
+            line["reference_gpu"] = ref_gpu
+            if "value" in ref_gpu:
+                line["reference_gpu"]["b200_over_reference_e2e"] = line["e2e"]["value"] / ref_gpu["value"]
         print(json.dumps(line), flush=True)
-    runner.exit()
     dist.destroy_process_group()
 
 
@@ -302,6 +367,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the cpu_baseline leg")
     ap.add_argument("--skip-nccl", action="store_true", help="omit the NCCL comparison of the row-parallel block")
+    ap.add_argument("--forward-compare", action="store_true", help="also time a restatement of the reference's decode forward (cuBLAS + NCCL + "
+                    "compiled elementwise) on the runner's weights; superseded by the run of the reference engine itself")
+    ap.add_argument("--skip-reference-gpu", action="store_true", help="omit the run of the unmodified reference engine on the GPUs")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -223,8 +223,11 @@ enum {
   B2_OPT_ROWPAR_FORM = 1,        /* B2_FORM_AUTO (default), _ONESHOT or _OWNER: what b2_rowpar_fused launches */
   B2_OPT_OWNER_MAX_TOKENS = 2,   /* AUTO: largest M the row-owner form takes at world >= 4 (default 64,
                                     at most oneshot_tokens)                                                    */
-  B2_OPT_TWOSHOT_MIN_TOKENS = 3  /* b2_rowpar_form answers B2_FORM_TWOSHOT from this M on (default 257 at
+  B2_OPT_TWOSHOT_MIN_TOKENS = 3, /* b2_rowpar_form answers B2_FORM_TWOSHOT from this M on (default 257 at
                                     world 2, 128 above)                                                        */
+  B2_OPT_WHOLE_TILES = 4         /* 1: fused row-parallel calls with more than 64 tokens whose output tiles fit
+                                    the SMs in one wave give every CTA one whole tile (no K split, no fp32
+                                    combine in L2); 0: stream-K split over all SMs                              */
 };
 int b2_ctx_set_option(b2_ctx* ctx, int option, int64_t value);
 /* Which entry point and form serve M rows of N features on this context:
@@ -396,8 +399,8 @@ typedef struct b2_gemm_plan {
  * [9 + S] for 64-token tiles = clusters of S CTAs the device holds at once
  * (on a GPU the library asks the occupancy calculator). */
 int b2_plan_gemm(int epilogue, int M, int N, int K, int num_sms, const int* resident_clusters, b2_gemm_plan* plan);
-/* The same with planner options: bit 0 = one whole tile per CTA when a many-token problem fits one wave (what the
- * environment variable B2_WHOLE_TILES=1 switches on for the library's own launches). */
+/* The same with planner options: bit 0 = one whole tile per CTA when a many-token problem fits one wave (what
+ * B2_OPT_WHOLE_TILES switches on for the fused row-parallel launches). */
 int b2_plan_gemm_opts(int epilogue, int M, int N, int K, int num_sms, const int* resident_clusters, int options,
                       b2_gemm_plan* plan);
 

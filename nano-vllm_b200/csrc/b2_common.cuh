@@ -365,6 +365,7 @@ struct b2_ctx {
   // which form of the fused row-parallel block b2_rowpar_fused launches (b2_ctx_set_option)
   int rowpar_form;         // B2_FORM_AUTO / ONESHOT / OWNER
   int owner_max_tokens;    // AUTO: the owner form serves up to this many tokens at world >= 4
+  bool whole_tiles;        // fused row-parallel calls in the token-row layout: one whole tile per CTA when the tiles fit one wave
   int twoshot_min_tokens;  // b2_rowpar_form: from this many tokens on callers should use b2_rowpar_fused_twoshot
 
   // rank-local scratch

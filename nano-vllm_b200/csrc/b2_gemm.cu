@@ -1747,18 +1747,11 @@ int pick_cluster_split(int bn, int tiles, int kblocks, int num_sms, Resident&& r
 }
 
 // Pure host arithmetic: no CUDA call besides what `resident` makes.
-constexpr int PLAN_WHOLE_TILES = 1;  // planner option, see whole_tiles_enabled()
+constexpr int PLAN_WHOLE_TILES = 1;  // planner option bit
 
-// B2_WHOLE_TILES=1 (opt-in until measured): a token-row problem whose tiles fit the device in one wave at some tile
-// width runs one whole tile per CTA instead of a stream-K split, whose fp32 combine in L2 costs more than the idle SMs
-// when the GEMM itself lasts a few microseconds (128-512 tokens of a two-shot call).
-bool whole_tiles_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("B2_WHOLE_TILES");
-    return e != nullptr && e[0] == '1';
-  }();
-  return on;
-}
+// Planner option PLAN_WHOLE_TILES (b2_ctx_set_option B2_OPT_WHOLE_TILES): a token-row problem whose tiles fit the device
+// in one wave at some tile width runs one whole tile per CTA instead of a stream-K split, whose fp32 combine in L2 costs
+// more than the idle SMs when the GEMM itself lasts a few microseconds (128-1024 tokens of a fused row-parallel call).
 
 template <class Resident>
 int plan_gemm(int epi, int M, int N, int K, int num_sms, int min_grid, int reducers, int64_t tile_cap, bool clusters_on,
@@ -1820,7 +1813,7 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
                               if constexpr (EPI == EPI_PUSH2 || EPI == EPI_SAMPLE) return 0;
                               else return bn == 32 ? max_resident_clusters<32, EPI>(S) : max_resident_clusters<64, EPI>(S);
                             },
-                            plan, whole_tiles_enabled() ? PLAN_WHOLE_TILES : 0);
+                            plan, (ctx->whole_tiles && is_push(EPI)) ? PLAN_WHOLE_TILES : 0);
   if (prc != B2_OK) return prc;
   const bool swap = plan.swap != 0;
   const int bn = plan.bn;
@@ -2230,6 +2223,9 @@ int b2_ctx_set_option(b2_ctx* ctx, int option, int64_t value) {
     case B2_OPT_OWNER_MAX_TOKENS:
       if (value < 0) return B2_ERR_ARG;
       ctx->owner_max_tokens = static_cast<int>(std::min<int64_t>(value, ctx->cfg.oneshot_tokens));
+      return B2_OK;
+    case B2_OPT_WHOLE_TILES:
+      ctx->whole_tiles = value != 0;
       return B2_OK;
     case B2_OPT_TWOSHOT_MIN_TOKENS:
       if (value < 1) return B2_ERR_ARG;

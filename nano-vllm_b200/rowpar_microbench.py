@@ -131,6 +131,7 @@ class ReferenceBlock:
             except Exception:
                 self._add_rms = _restated_add_rms
 
+    @torch.inference_mode()  # as the reference runs its model (nanovllm/engine/model_runner.py:195)
     def __call__(self, x, w, residual):
         if self.linear is not None:
             self.linear.weight.data = w
@@ -141,12 +142,16 @@ class ReferenceBlock:
         return self._add_rms(y, residual, self.norm_w, self.eps)
 
 
-def _error_stats(got: torch.Tensor, ref: torch.Tensor) -> dict:
+def _error_stats(got: torch.Tensor, ref: torch.Tensor, unit_scale: bool = True) -> dict:
+    """Per element |err| <= abs + rel |ref|.  abs = 2e-2 for unit-scale rows (the normalised output); for the
+    un-normalised residual sum, whose size grows with K, abs = 2e-2 x the row's RMS (when that exceeds 1): the bf16
+    partial products that cross NVLink carry half a unit in the last place of THEIR size even where they cancel."""
     got, ref = got.float(), ref.float()
     err = (got - ref).abs()
     big = ref.abs() >= 1.0
+    scale = 1.0 if unit_scale else ref.pow(2).mean(-1, keepdim=True).sqrt().clamp_min(1.0)
     return {"max_abs_err": err.max().item(), "max_rel_err": (err[big] / ref.abs()[big]).max().item() if bool(big.any()) else 0.0,
-            "within_tolerance": bool((err <= TOL_ABS + TOL_REL * ref.abs()).all())}
+            "within_tolerance": bool((err <= TOL_ABS * scale + TOL_REL * ref.abs()).all())}
 
 
 def compare_blocks(blocks, peaks: dict, iters: int = 200, with_nccl: bool = True, forms: bool = False) -> dict:
@@ -180,7 +185,17 @@ def compare_blocks(blocks, peaks: dict, iters: int = 200, with_nccl: bool = True
             for f, label in ((_abi.FORM_ONESHOT, "oneshot_us"), (_abi.FORM_OWNER, "owner_us")):
                 rt.set_option(_abi.OPT_ROWPAR_FORM, f)
                 row[label] = time_in_graph(ours_call, n_w, iters)
+            if m > 64:  # token-row layout: with one whole tile per CTA instead of the stream-K split
+                rt.set_option(_abi.OPT_WHOLE_TILES, 1)
+                row["owner_whole_tiles_us"] = time_in_graph(ours_call, n_w, iters)
+                rt.set_option(_abi.OPT_WHOLE_TILES, 0)
             rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_AUTO)
+            if n == rt.hidden and m >= 16:
+                rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, 1)
+                row["twoshot_us"] = time_in_graph(ours_call, n_w, iters)
+                rt.set_option(_abi.OPT_WHOLE_TILES, 1)
+                row["twoshot_whole_tiles_us"] = time_in_graph(ours_call, n_w, iters)
+                rt.set_option(_abi.OPT_WHOLE_TILES, 0)
             rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, 257 if world <= 2 else 128)
         row.update(roofline_us(m, n, kr, world, peaks))
         row["frac_of_roof"] = row["roof_us"] / ours
@@ -195,7 +210,7 @@ def compare_blocks(blocks, peaks: dict, iters: int = 200, with_nccl: bool = True
         exact = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * norm_w.float()
         row["parity_vs_fp32"] = _error_stats(normed, exact)
         if form != _abi.FORM_TWOSHOT:  # (the two-shot form keeps the residual row-sharded)
-            row["parity_vs_fp32"]["residual_within_tolerance"] = _error_stats(new_res, s)["within_tolerance"]
+            row["parity_vs_fp32"]["residual_within_tolerance"] = _error_stats(new_res, s, unit_scale=False)["within_tolerance"]
         if with_nccl and world > 1:
             try:
                 ref = ReferenceBlock(n, kr * world, kr, norm_w, 1e-6, dev)

@@ -153,7 +153,7 @@ def test_planner_choices_for_the_decode_shapes(pkg):
 @pytest.mark.parametrize("epi,m,n,k", [(EPI_PUSH2, 256, 5120, 1024), (EPI_PUSH2, 512, 5120, 3200), (EPI_STORE, 300, 4096, 4096),
                                        (EPI_PUSH2, 1024, 5120, 1024), (EPI_STORE, 8192, 5120, 1024)])
 def test_whole_tile_option(pkg, epi, m, n, k):
-    """Planner option 1 (B2_WHOLE_TILES=1): a many-token problem that fits one wave of tiles at some tile width gets one
+    """Planner option 1 (B2_OPT_WHOLE_TILES): a many-token problem that fits one wave of tiles at some tile width gets one
     whole tile per CTA - nothing is split, so no fp32 combine - and everything else is planned as before."""
     from nanovllm_b200 import _abi
     rc, base = plan_gemm(_abi, epi, m, n, k)
