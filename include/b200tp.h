@@ -196,16 +196,15 @@ int b2_gemm_static_scratch(const void* A, int64_t lda, const void* W, int64_t ld
  * and arithmetic (every rank ends up with all rows of both outputs):
  *   one-shot   every rank receives every rank's partial and reduces all rows
  *              itself: one NVLink store latency, (world-1) M N 2 bytes sent
- *              per rank.  Used at world 2, and for more tokens than the
- *              owner form is set to take.
+ *              per rank.  Used for up to 64 tokens (decode) and on one rank.
  *   row-owner  token row t is reduced by rank t mod world only: partial rows
  *              go to their owner, which sums, adds the residual, normalises
  *              and sends the finished row and the new residual row to every
- *              rank: two NVLink store latencies, about
- *              3 (world-1)/world M N 2 bytes sent per rank.  Used at world
- *              >= 4 for up to 64 tokens (decode) unless set otherwise with
- *              b2_ctx_set_option.  -0.0 in an output of this form is stored
- *              as +0.0. */
+ *              rank: two NVLink store latencies and two system-scope fences,
+ *              about 3 (world-1)/world M N 2 bytes sent per rank.  Used at
+ *              world >= 4 for 65 .. min(1024, oneshot_tokens) tokens unless
+ *              set otherwise with b2_ctx_set_option.  -0.0 in an output of
+ *              this form is stored as +0.0. */
 int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias,
                     int M, int N, int Kr, const void* residual_in, const void* norm_w, float eps,
                     void* normed_out, void* residual_out, void* stream);
@@ -221,13 +220,14 @@ enum {
 };
 enum {
   B2_OPT_ROWPAR_FORM = 1,        /* B2_FORM_AUTO (default), _ONESHOT or _OWNER: what b2_rowpar_fused launches */
-  B2_OPT_OWNER_MAX_TOKENS = 2,   /* AUTO: largest M the row-owner form takes at world >= 4 (default 64,
-                                    at most oneshot_tokens)                                                    */
-  B2_OPT_TWOSHOT_MIN_TOKENS = 3, /* b2_rowpar_form answers B2_FORM_TWOSHOT from this M on (default 257 at
-                                    world 2, 128 above)                                                        */
-  B2_OPT_WHOLE_TILES = 4         /* 1: fused row-parallel calls with more than 64 tokens whose output tiles fit
-                                    the SMs in one wave give every CTA one whole tile (no K split, no fp32
-                                    combine in L2); 0: stream-K split over all SMs                              */
+  B2_OPT_OWNER_MAX_TOKENS = 2,   /* AUTO: largest M the row-owner form takes (default min(1024, oneshot_tokens)) */
+  B2_OPT_TWOSHOT_MIN_TOKENS = 3, /* b2_rowpar_form answers B2_FORM_TWOSHOT from this M on (default: the
+                                    row-owner form's largest M + 1)                                            */
+  B2_OPT_OWNER_MIN_TOKENS = 5,   /* AUTO: smallest M the row-owner form takes at world >= 4 (default 65: decode-
+                                    sized calls stay on the one-shot form)                                     */
+  B2_OPT_WHOLE_TILES = 4         /* 1 (default): fused row-parallel calls with more than 64 tokens whose output tiles fit
+                                    the SMs in one wave, and whose K is at most 6144, give every CTA one whole tile (no K split, no fp32
+                                    combine in L2); 0: always a stream-K split over all SMs                      */
 };
 int b2_ctx_set_option(b2_ctx* ctx, int option, int64_t value);
 /* Which entry point and form serve M rows of N features on this context:

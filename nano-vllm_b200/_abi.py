@@ -22,7 +22,7 @@ lib = C.CDLL(LIB_PATH)
 OK, ERR_ARG, ERR_SHAPE, ERR_CUDA, ERR_STATE, ERR_TIMEOUT, ERR_UNSUPPORTED = range(7)
 HANDLE_BYTES = 64
 FORM_AUTO, FORM_ONESHOT, FORM_OWNER, FORM_TWOSHOT = range(4)
-OPT_ROWPAR_FORM, OPT_OWNER_MAX_TOKENS, OPT_TWOSHOT_MIN_TOKENS, OPT_WHOLE_TILES = 1, 2, 3, 4
+OPT_ROWPAR_FORM, OPT_OWNER_MAX_TOKENS, OPT_TWOSHOT_MIN_TOKENS, OPT_WHOLE_TILES, OPT_OWNER_MIN_TOKENS = 1, 2, 3, 4, 5
 _ERR_NAMES = {1: "bad argument", 2: "shape outside what the context was created for", 3: "CUDA error",
               4: "bad state (peers not imported?)", 5: "device-side wait timed out", 6: "unsupported"}
 WAIT_NAMES = {0: "none", 1: "GEMM: TMA stage never filled", 2: "GEMM: stage never freed", 3: "GEMM: accumulator never completed",

@@ -67,6 +67,16 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
+// Has more than `limit_ns` passed since t0?  The 64-bit timer is not read in one piece on every part: a value read
+// while its low half wraps can be off by 2^32 ns in either direction.  A limit counts as passed only if two
+// successive readings both say so and neither lies before t0.
+__device__ __forceinline__ bool time_limit_passed(uint64_t t0, uint64_t limit_ns) {
+  const uint64_t a = globaltimer_ns();
+  if (a < t0 || a - t0 <= limit_ns) return false;
+  const uint64_t b = globaltimer_ns();
+  return b >= a && b - t0 > limit_ns;
+}
+
 __device__ __forceinline__ void report_timeout(B2Status* st, int detail) {
   // the word is in mapped host memory; concurrent reporters write the same code
   if (st != nullptr) {
@@ -147,7 +157,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 0x3FF) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > limit_ns) {
+      if (time_limit_passed(t0, limit_ns)) {
         *abort_flag = code;
         return false;
       }
@@ -364,7 +374,8 @@ struct b2_ctx {
 
   // which form of the fused row-parallel block b2_rowpar_fused launches (b2_ctx_set_option)
   int rowpar_form;         // B2_FORM_AUTO / ONESHOT / OWNER
-  int owner_max_tokens;    // AUTO: the owner form serves up to this many tokens at world >= 4
+  int owner_min_tokens;    // AUTO: the row-owner form serves owner_min_tokens .. owner_max_tokens tokens at world >= 2
+  int owner_max_tokens;
   bool whole_tiles;        // fused row-parallel calls in the token-row layout: one whole tile per CTA when the tiles fit one wave
   int twoshot_min_tokens;  // b2_rowpar_form: from this many tokens on callers should use b2_rowpar_fused_twoshot
 

@@ -114,8 +114,10 @@ int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
   if (c->cfg.oneshot_tokens > c->cfg.max_tokens) c->cfg.oneshot_tokens = c->cfg.max_tokens;
   if (c->cfg.timeout_ms <= 0) c->cfg.timeout_ms = 5000;
   c->rowpar_form = B2_FORM_AUTO;
-  c->owner_max_tokens = std::min(64, c->cfg.oneshot_tokens);
-  c->twoshot_min_tokens = c->cfg.world <= 2 ? 257 : 128;
+  c->owner_min_tokens = 65;
+  c->owner_max_tokens = std::min(1024, c->cfg.oneshot_tokens);
+  c->twoshot_min_tokens = c->owner_max_tokens + 1;
+  c->whole_tiles = true;
   const int rc = ctx_init(c);
   if (rc != B2_OK) {
     b2_ctx_destroy(c);  // frees whatever was allocated before the failing call; the error text stays

@@ -303,7 +303,7 @@ __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
       for (uint32_t it = 1;; ++it) {
         val = b2::ld_volatile_v4(src);
         if (!b2::has_sentinel(val)) break;
-        if ((it & 0xFF) == 0 && b2::globaltimer_ns() - t0 > a.timeout_ns) {
+        if ((it & 0xFF) == 0 && b2::time_limit_passed(t0, a.timeout_ns)) {
           b2::report_timeout(a.status, B2_WAIT_EMBED);
           break;
         }
@@ -411,7 +411,7 @@ __global__ void __launch_bounds__(256) broadcast_tokens_kernel(const BcastArgs a
       if (v < 0) {
         const uint64_t t0 = b2::globaltimer_ns();
         for (uint32_t it = 1; (v = *src) < 0; ++it) {
-          if ((it & 0xFF) == 0 && b2::globaltimer_ns() - t0 > a.timeout_ns) {
+          if ((it & 0xFF) == 0 && b2::time_limit_passed(t0, a.timeout_ns)) {
             b2::report_timeout(a.status, B2_WAIT_TOKENS);
             v = 0;
             break;

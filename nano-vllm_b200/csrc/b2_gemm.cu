@@ -599,9 +599,8 @@ __device__ __forceinline__ int reduce_rows(const GemmArgs& a, unsigned int parit
         if (pending && (spin & 0x3F) == 0x3F) {
           // one expired wait ends every later wait of this CTA at once
           if (*gave_up) break;
-          const uint64_t now = b2::globaltimer_ns();
-          if (t0 == 0) t0 = now;
-          else if (now - t0 > a.timeout_ns) {
+          if (t0 == 0) t0 = b2::globaltimer_ns();
+          else if (b2::time_limit_passed(t0, a.timeout_ns)) {
             *gave_up = 1;
             b2::report_timeout(a.status, B2_WAIT_PARTIALS);
             break;
@@ -712,9 +711,8 @@ __device__ __forceinline__ void collect_landed_rows(const GemmArgs& a, unsigned 
       }
       if (pending && (spin & 0x3F) == 0x3F) {
         if (*gave_up) return;
-        const uint64_t now = b2::globaltimer_ns();
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > a.timeout_ns) {
+        if (t0 == 0) t0 = b2::globaltimer_ns();
+        else if (b2::time_limit_passed(t0, a.timeout_ns)) {
           *gave_up = 1;
           b2::report_timeout(a.status, B2_WAIT_ROWS);
           return;
@@ -738,6 +736,13 @@ template <int EPI>
 __device__ __forceinline__ void fused_tail(const GemmArgs& a, unsigned int parity, float* red, volatile int* abort_flag, int aborted) {
   if (threadIdx.x == 0) stamp(a, 5);
   if (is_push(EPI)) {
+    // Every partial row of this CTA is on its way: from here on the CTA only waits for data, so the next kernel's CTAs
+    // may take the SMs that are free.  (Released at set-up instead, they could occupy SMs before all CTAs of this
+    // grid are resident, while the resident ones spin on rows the missing ones have yet to produce.)
+// Row-owner form: every rank waits for every other rank inside the same launch, so a store to a peer that lingers in
+    // a write buffer until the kernel ends would never leave: push the partial rows out before waiting for anything.
+    if (EPI == EPI_PUSH3) __threadfence_system();
+        if (threadIdx.x == 0) b2::pdl_launch_dependents();
     if (!aborted) {
       if (EPI == EPI_PUSH) {
         switch (a.world) {
@@ -753,6 +758,7 @@ __device__ __forceinline__ void fused_tail(const GemmArgs& a, unsigned int parit
           case 4: reduce_rows<4, FORM_OWNER>(a, parity, red, abort_flag); break;
           default: reduce_rows<8, FORM_OWNER>(a, parity, red, abort_flag); break;
         }
+        __threadfence_system();  // the finished rows leave for the peers now (see above)
         if (threadIdx.x == 0) stamp(a, 4);  // owned rows finished and sent (overwrites "epilogue done": the GEMM part's end is stamp 5)
         collect_landed_rows(a, parity, abort_flag);
       } else {
@@ -780,7 +786,7 @@ __device__ __forceinline__ void fused_tail(const GemmArgs& a, unsigned int parit
             unsigned int got;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(cnt) : "memory");
             if (got >= expect) break;
-            if ((spin & 0xFF) == 0xFF && b2::globaltimer_ns() - t0 > a.timeout_ns) {
+            if ((spin & 0xFF) == 0xFF && b2::time_limit_passed(t0, a.timeout_ns)) {
               b2::report_timeout(a.status, B2_WAIT_ROWS);
               break;
             }
@@ -873,8 +879,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
   __syncthreads();
   b2::tc_fence_after();
   const uint32_t tmem_base = has_gemm ? *tmem_slot : 0;
-  // the next kernel in the stream may start its own set-up from now on
-  if (threadIdx.x == 0) b2::pdl_launch_dependents();
+  // The next kernel in the stream may start its own set-up from now on - unless this launch is a fused row-parallel
+  // call: its CTAs later wait for rows that other CTAs of the same grid (and of the peers' grids) produce, so the
+  // dependents are released only once every CTA has delivered its part (fused_tail), when nothing of this grid
+  // needs an SM any more.
+  if (threadIdx.x == 0 && !is_push(EPI)) b2::pdl_launch_dependents();
   if (threadIdx.x == 0) stamp(a, 0);
   unsigned int parity = 0;
 
@@ -924,6 +933,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
       // ---------------- MMA issuer ----------------
       if (lane == 0) {
         constexpr uint32_t idesc = b2::umma_idesc_bf16(BN);
+        // The first stage cannot fill before the earlier kernels have completed (the activations are fetched after the
+        // producer's dependency wait): wait for them here, so that the pipeline's time limit measures the pipeline
+        // alone and not an earlier kernel that is itself waiting for a peer.
+        b2::pdl_wait();
         int stage = 0;
         uint32_t phase = 0;
         int u = 0, seg = 0;
@@ -1133,7 +1146,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
   __syncthreads();
   b2::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) b2::pdl_launch_dependents();
+  if (threadIdx.x == 0 && !is_push(EPI)) b2::pdl_launch_dependents();  // fused row-parallel calls: later, see fused_tail
   if (threadIdx.x == 0) stamp(a, 0);
   unsigned int parity = 0;
   // fused qkv heads: rotary factors and cache slots of the first rows this warp will finish, fetched while the
@@ -1172,6 +1185,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = b2::umma_idesc_bf16(BN);
+      b2::pdl_wait();  // the pipeline's time limit must not include the wait for earlier kernels
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -1483,7 +1497,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant_
   b2::cluster_wait();
   b2::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) b2::pdl_launch_dependents();
+  if (threadIdx.x == 0 && !is_push(EPI)) b2::pdl_launch_dependents();  // fused row-parallel calls: later, see fused_tail
   if (threadIdx.x == 0) stamp(a, 0);
   unsigned int parity = 0;
 
@@ -1529,6 +1543,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant_
     // ---------------- MMA issuer (even CTA only) ----------------
     if (lane == 0 && cr == 0) {
       constexpr uint32_t idesc = b2::umma_idesc_bf16_pair(BN);
+      b2::pdl_wait();  // the pipeline's time limit must not include the wait for earlier kernels
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -1761,7 +1776,8 @@ int plan_gemm(int epi, int M, int N, int K, int num_sms, int min_grid, int reduc
   if (p.swap) p.bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   else p.bn = (N >= 256) ? 256 : (N > 64 ? 128 : 64);
   bool one_tile_per_cta = false;
-  if (!p.swap && (options & PLAN_WHOLE_TILES)) {
+  // (a whole tile per CTA means the CTA walks the whole K range alone: worth it only while that range is short)
+  if (!p.swap && (options & PLAN_WHOLE_TILES) && (K + BK - 1) / BK <= 96) {
     const int sms = epi == EPI_PUSH2 ? std::max(1, num_sms - reducers) : num_sms;
     for (int bn = 64; bn <= p.bn; bn *= 2) {  // the narrowest tile that still fits one wave gives the most parallelism
       const int64_t t = static_cast<int64_t>((M + BM - 1) / BM) * ((N + bn - 1) / bn);
@@ -1813,7 +1829,7 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
                               if constexpr (EPI == EPI_PUSH2 || EPI == EPI_SAMPLE) return 0;
                               else return bn == 32 ? max_resident_clusters<32, EPI>(S) : max_resident_clusters<64, EPI>(S);
                             },
-                            plan, (ctx->whole_tiles && is_push(EPI)) ? PLAN_WHOLE_TILES : 0);
+                            plan, (ctx->whole_tiles && (EPI == EPI_PUSH2 || EPI == EPI_PUSH3)) ? PLAN_WHOLE_TILES : 0);
   if (prc != B2_OK) return prc;
   const bool swap = plan.swap != 0;
   const int bn = plan.bn;
@@ -1932,7 +1948,7 @@ __global__ void lm_head_sync_kernel(int rank, int world, unsigned int* flags_ran
         unsigned int got;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(flags_rank0 + r) : "memory");
         if (static_cast<int>(got - want) >= 0) break;
-        if ((spin & 0xFF) == 0xFF && b2::globaltimer_ns() - t0 > timeout_ns) {
+        if ((spin & 0xFF) == 0xFF && b2::time_limit_passed(t0, timeout_ns)) {
           b2::report_timeout(status, B2_WAIT_LOGITS);
           break;
         }
@@ -1973,7 +1989,7 @@ __global__ void __launch_bounds__(256) sample_finish_kernel(int rank, int world,
             unsigned int got;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(flags_rank0 + r) : "memory");
             if (static_cast<int>(got - want) >= 0) break;
-            if ((spin & 0xFF) == 0xFF && b2::globaltimer_ns() - t0 > timeout_ns) {
+            if ((spin & 0xFF) == 0xFF && b2::time_limit_passed(t0, timeout_ns)) {
               b2::report_timeout(status, B2_WAIT_LOGITS);
               break;
             }
@@ -2200,12 +2216,19 @@ int b2_rowpar_fused_twoshot(b2_ctx* ctx, const void* A, int64_t lda, const void*
   return launch_gemm<EPI_PUSH2>(ctx, A, lda, W, ldw, M, N, Kr, args, args.rows_per_rank, static_cast<cudaStream_t>(stream));
 }
 
+// AUTO: the one-shot form for decode-sized calls (one NVLink store latency; its bytes are few) and at 1 or 2 ranks (one
+// copy to send either way); at 4 ranks and more the row-owner form from owner_min_tokens to owner_max_tokens tokens,
+// where sending every partial to every rank and reducing every row on every rank costs more than the second hop.
+static int auto_form(const b2_ctx* ctx, int m) {
+  return (ctx->cfg.world >= 4 && m >= ctx->owner_min_tokens && m <= ctx->owner_max_tokens) ? B2_FORM_OWNER : B2_FORM_ONESHOT;
+}
+
 // Which form of the fused row-parallel block serves M tokens on this context (B2_FORM_*).
 static int rowpar_form_for(const b2_ctx* ctx, int M, int N) {
   const int world = ctx->cfg.world;
   if (world >= 2 && M >= ctx->twoshot_min_tokens && N == ctx->cfg.hidden && M <= ctx->cfg.max_tokens) return B2_FORM_TWOSHOT;
   if (ctx->rowpar_form == B2_FORM_ONESHOT || ctx->rowpar_form == B2_FORM_OWNER) return ctx->rowpar_form;
-  return (world >= 4 && M <= ctx->owner_max_tokens) ? B2_FORM_OWNER : B2_FORM_ONESHOT;
+  return auto_form(ctx, M);
 }
 
 int b2_rowpar_form(b2_ctx* ctx, int M, int N) {
@@ -2223,6 +2246,10 @@ int b2_ctx_set_option(b2_ctx* ctx, int option, int64_t value) {
     case B2_OPT_OWNER_MAX_TOKENS:
       if (value < 0) return B2_ERR_ARG;
       ctx->owner_max_tokens = static_cast<int>(std::min<int64_t>(value, ctx->cfg.oneshot_tokens));
+      return B2_OK;
+    case B2_OPT_OWNER_MIN_TOKENS:
+      if (value < 1) return B2_ERR_ARG;
+      ctx->owner_min_tokens = static_cast<int>(std::min<int64_t>(value, 1 << 30));
       return B2_OK;
     case B2_OPT_WHOLE_TILES:
       ctx->whole_tiles = value != 0;
@@ -2254,7 +2281,7 @@ int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int6
     const int m = std::min(chunk, M - m0);
     // the owner form when it is cheaper (or forced); every rank decides alike: the choice depends on M and the context only
     int form = ctx->rowpar_form;
-    if (form == B2_FORM_AUTO) form = (world >= 4 && m <= ctx->owner_max_tokens) ? B2_FORM_OWNER : B2_FORM_ONESHOT;
+    if (form == B2_FORM_AUTO) form = auto_form(ctx, m);
     GemmArgs args{};
     args.bias = (ctx->cfg.rank == 0) ? static_cast<const uint16_t*>(bias) : nullptr;  // bias enters the sum once
     args.world = world;

@@ -176,27 +176,42 @@ def compare_blocks(blocks, peaks: dict, iters: int = 200, with_nccl: bool = True
         def ours_call(i):
             return ops.rowpar_fused(x, ws[i % n_w], None, residual, norm_w, 1e-6)
 
+        def timed(label):
+            """One timing; an expired device-side wait is reported in the row and the context reset on every rank."""
+            us = time_in_graph(ours_call, n_w, iters)
+            flag = torch.zeros(1, dtype=torch.int32)
+            try:
+                rt.check_status()
+            except _abi.B2Error as ex:
+                flag[0] = 1
+                row.setdefault("errors", {})[label] = str(ex)
+            if world > 1:
+                dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            if flag.item():
+                row.setdefault("errors", {}).setdefault(label, "a wait expired on another rank")
+                rt.poisoned = True
+                rt.reset()
+            return us
+
         form = ops.rowpar_form(m, n)
-        ours = time_in_graph(ours_call, n_w, iters)
-        row = {"M": m, "N": n, "Kr": kr, "tp": world, "b200_us": ours,
-               "form": {_abi.FORM_ONESHOT: "one-shot", _abi.FORM_OWNER: "row-owner", _abi.FORM_TWOSHOT: "two-shot"}[form]}
+        row = {}
+        ours = timed("auto")
+        row.update({"M": m, "N": n, "Kr": kr, "tp": world, "b200_us": ours,
+                    "form": {_abi.FORM_ONESHOT: "one-shot", _abi.FORM_OWNER: "row-owner", _abi.FORM_TWOSHOT: "two-shot"}[form]})
         if forms and world > 1 and m <= rt.oneshot_tokens:
             rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, 1 << 30)
             for f, label in ((_abi.FORM_ONESHOT, "oneshot_us"), (_abi.FORM_OWNER, "owner_us")):
                 rt.set_option(_abi.OPT_ROWPAR_FORM, f)
-                row[label] = time_in_graph(ours_call, n_w, iters)
-            if m > 64:  # token-row layout: with one whole tile per CTA instead of the stream-K split
-                rt.set_option(_abi.OPT_WHOLE_TILES, 1)
-                row["owner_whole_tiles_us"] = time_in_graph(ours_call, n_w, iters)
+                row[label] = timed(label)
+            if m > 64:  # token-row layout: with the stream-K split instead of one whole tile per CTA
                 rt.set_option(_abi.OPT_WHOLE_TILES, 0)
+                row["owner_streamk_us"] = timed("owner_streamk_us")
+                rt.set_option(_abi.OPT_WHOLE_TILES, 1)
             rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_AUTO)
             if n == rt.hidden and m >= 16:
                 rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, 1)
-                row["twoshot_us"] = time_in_graph(ours_call, n_w, iters)
-                rt.set_option(_abi.OPT_WHOLE_TILES, 1)
-                row["twoshot_whole_tiles_us"] = time_in_graph(ours_call, n_w, iters)
-                rt.set_option(_abi.OPT_WHOLE_TILES, 0)
-            rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, 257 if world <= 2 else 128)
+                row["twoshot_us"] = timed("twoshot_us")
+            rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, rt.default_twoshot_min_tokens)
         row.update(roofline_us(m, n, kr, world, peaks))
         row["frac_of_roof"] = row["roof_us"] / ours
         row["nvlink_egress_gbs"] = row["nvlink_bytes"] / (ours * 1e-6) / 1e9 if world > 1 else 0.0

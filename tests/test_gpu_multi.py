@@ -81,7 +81,7 @@ def _worker(rank: int, world: int, port: int):
                 own_n, own_s = ops.rowpar_fused(*args)
             y = ops.rowpar_fused(xs[rank].to(dev), ws[rank].to(dev), None, None, None, 0.0)
             rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_AUTO)
-            rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, 257 if world <= 2 else 128)
+            rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, rt.default_twoshot_min_tokens)
             torch.cuda.synchronize()
             rt.check_status()
             exact_n, exact_s = O.fused_row_parallel_norm_exact(xs, ws, residual, norm_w, 1e-6)
@@ -102,6 +102,7 @@ def _worker(rank: int, world: int, port: int):
         assert_close_bf16(normed, O.fused_row_parallel_norm_exact(xs, ws, residual, norm_w, 1e-6)[0], "61 launches of alternating forms")
 
         # ---- two-shot form (many tokens): normed rows everywhere, the residual only on the rows a rank owns ----
+        rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, 128)  # this section is about the two-shot kernel: give it these sizes
         for i, (m, k) in enumerate([(1024, 2048), (300, 1024), (4096, 1024), (777, 2048)] if big else [(512, 1024), (300, 1024), (1040, 1024)]):
             n = H
             xs, ws, residual, norm_w = O.rowpar_case(m, k, n, world, seed=300 + i)
@@ -124,6 +125,7 @@ def _worker(rank: int, world: int, port: int):
         y = ops.rowpar_fused(xs[rank].to(dev), ws[rank].to(dev), None, None, None, 0.0)  # plain forward through the two-shot kernel
         assert_close_bf16(y, sum(x.float() @ w.float().t() for x, w in zip(xs, ws)), "two-shot plain forward")
         rt.check_status()
+        rt.set_option(_abi.OPT_TWOSHOT_MIN_TOKENS, rt.default_twoshot_min_tokens)
 
         # ---- plain RowParallelLinear.forward with a bias (added once, by rank 0) ----
         xs, ws, _, _ = O.rowpar_case(48, 1024, 1024, world, seed=7)

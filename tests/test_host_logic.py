@@ -150,7 +150,7 @@ def test_planner_choices_for_the_decode_shapes(pkg):
     assert _abi.lib.b2_plan_gemm(0, 64, 64, 64, SMS, None, None) == 1
 
 
-@pytest.mark.parametrize("epi,m,n,k", [(EPI_PUSH2, 256, 5120, 1024), (EPI_PUSH2, 512, 5120, 3200), (EPI_STORE, 300, 4096, 4096),
+@pytest.mark.parametrize("epi,m,n,k", [(EPI_PUSH2, 256, 5120, 1024), (EPI_PUSH2, 512, 5120, 3200), (EPI_STORE, 300, 4096, 4096), (EPI_PUSH3, 256, 5120, 12800),
                                        (EPI_PUSH2, 1024, 5120, 1024), (EPI_STORE, 8192, 5120, 1024)])
 def test_whole_tile_option(pkg, epi, m, n, k):
     """Planner option 1 (B2_OPT_WHOLE_TILES): a many-token problem that fits one wave of tiles at some tile width gets one
@@ -162,7 +162,7 @@ def test_whole_tile_option(pkg, epi, m, n, k):
     check_plan(_abi, opt, m, n, k)
     row_tiles = (m + 127) // 128
     fits = [bn for bn in (64, 128, 256) if bn <= base.bn and row_tiles * ((n + bn - 1) // bn) <= SMS]
-    if base.swap or not fits:
+    if base.swap or not fits or (k + 63) // 64 > 96:   # (a long K range is never given to one CTA alone)
         assert [getattr(opt, f) for f, _ in opt._fields_] == [getattr(base, f) for f, _ in base._fields_]
     else:
         assert opt.bn == fits[0] and opt.round_robin == 1 and opt.gemm_ctas == opt.tiles_p * opt.tiles_q
