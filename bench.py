@@ -370,7 +370,14 @@ def main():
     ap.add_argument("--forward-compare", action="store_true", help="also time a restatement of the reference's decode forward (cuBLAS + NCCL + "
                     "compiled elementwise) on the runner's weights; superseded by the run of the reference engine itself")
     ap.add_argument("--skip-reference-gpu", action="store_true", help="omit the run of the unmodified reference engine on the GPUs")
+    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "cfg2", "cfg5"],
+                    help="decode8b: Qwen3-8B decode (the headline metric); cfg2: the reference bench.py workload (Qwen3-0.6B); cfg5: Qwen3-32B long prefill")
     args = ap.parse_args()
+    if args.workload != "decode8b" and args.impl == "b200":
+        import bench_workloads
+        pk, _ = peaks()
+        (bench_workloads.run_cfg2 if args.workload == "cfg2" else bench_workloads.run_cfg5)(args, pk, ClockSampler)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -10,7 +10,6 @@ in token lists and block tables (every rank must be given the same batch).
 """
 from __future__ import annotations
 
-import os
 from dataclasses import dataclass, field
 
 import torch
@@ -87,11 +86,9 @@ class ModelRunner:
         self.block_size = kvcache_block_size
         self.max_num_seqs, self.max_model_len, self.max_num_batched_tokens = max_num_seqs, max_model_len, max_num_batched_tokens
         self.enforce_eager = enforce_eager
-        # LM head and sampler in one pass (no [B, vocab] logits, no gather).  B2_FUSED_SAMPLER=0/1 forces it off/on;
-        # by default it is on at the world sizes it has been run and measured at (1 and 2 GPUs)
-        env = os.environ.get("B2_FUSED_SAMPLER")
+        # LM head and sampler in one pass (no [B, vocab] logits, no gather): the default at every world size
         if fused_sampler is None:
-            fused_sampler = (env != "0") if env is not None else self.world <= 2
+            fused_sampler = True
         self.fused_sampler = fused_sampler
         self.sample_seed = sample_seed
         self.device = torch.device("cuda", torch.cuda.current_device())
