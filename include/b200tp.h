@@ -416,7 +416,7 @@ int b2_plan_cta_units(const b2_gemm_plan* plan, int cta, int* units, int cap);
 int b2_plan_tile_contributors(const b2_gemm_plan* plan, int tile, int* first_cta, int* last_cta);
 
 /* Which kernel the calling thread's most recent GEMM-shaped call launched: 0 = persistent stream-K kernel,
- * 1 = cluster split-K kernel, 2 = CTA-pair kernel (opt-in: environment B2_PAIR=1, many-token problems only). */
+ * 1 = cluster split-K kernel, 2 = CTA-pair kernel (problems of at least 512 tokens). */
 int b2_last_gemm_kernel(void);
 
 /* Two-shot row ownership: the rank that reduces token row `token` (blocks of

@@ -82,7 +82,6 @@ struct GemmArgs {
   int tilesP, tilesQ, kblocks;
   int gemm_ctas;  // the first gemm_ctas CTAs of the grid share the GEMM units
   int round_robin;  // 1: whole tiles dealt round-robin instead of a stream-K range
-  int dedicated_reducers;  // two-shot: 1 = the CTAs past gemm_ctas reduce from the start and the GEMM CTAs never do
   int M, N;       // tokens, features of the output
   // EPI_STORE
   uint16_t* C;
@@ -543,18 +542,11 @@ __device__ __forceinline__ int reduce_rows(const GemmArgs& a, unsigned int parit
   unsigned char* my = a.inbox[a.rank] + parity * a.parity_stride;
   const uint4 sentinel = make_uint4(B2_SENTINEL32, B2_SENTINEL32, B2_SENTINEL32, B2_SENTINEL32);
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
-  // Every CTA takes rows blockIdx, blockIdx + grid, ... once its GEMM work is done.  Two-shot with
-  // dedicated reducers: only the CTAs past the GEMM CTAs reduce; they start at once and follow the GEMM's
-  // sweep over the token rows (worth it only when NVLink, not SM time, bounds the call).
+  // Every CTA takes rows blockIdx, blockIdx + grid, ... once its GEMM work is done.  (Setting CTAs aside that only
+  // reduce, following the GEMM's sweep over the rows, was measured and lost: a CTA reduces a row in about 5 us,
+  // latency-bound, so few reducers cannot keep up and many cost the GEMM its SMs.)
   int n_rows = a.M, row0 = blockIdx.x, row_step = gridDim.x;
-  if (TWO) {
-    n_rows = owned_rows(a.M, a.world, a.rank);
-    if (a.dedicated_reducers && static_cast<int>(gridDim.x) > a.gemm_ctas) {
-      row0 = static_cast<int>(blockIdx.x) - a.gemm_ctas;
-      row_step = static_cast<int>(gridDim.x) - a.gemm_ctas;
-      if (row0 < 0) row0 = n_rows;  // a GEMM CTA: nothing to reduce
-    }
-  }
+  if (TWO) n_rows = owned_rows(a.M, a.world, a.rank);
   if (FORM == FORM_OWNER) n_rows = owned_rows3(a.M, a.world, a.rank);
   int rows_done = 0;
   for (int row = row0; row < n_rows; row += row_step, ++rows_done) {
@@ -1429,8 +1421,7 @@ struct PerDeviceOnce {
 //   - even CTA:   its MMA thread (warp 1) waits on "full", issues the MMAs for the pair, and signals "stage
 //                 free" and "accumulator ready" to both CTAs with multicast commits.
 //   - odd CTA:    its epilogue warps report "accumulator drained" to the even CTA's barrier.
-// Whole 256 x BN tiles are dealt round-robin to the pairs (no K split).  Not yet a default path: it is used only
-// when the environment has B2_PAIR=1.
+// Whole 256 x BN tiles are dealt round-robin to the pairs (no K split).  The default for at least 512 tokens.
 // ---------------------------------------------------------------------------
 template <int BN>
 struct CfgPair {
@@ -1668,10 +1659,12 @@ int launch_pair_inst(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmA
   return B2_OK;
 }
 
+// The CTA-pair kernel serves many-token problems (at least 512 tokens, tiles of 128 or 256 features); B2_PAIR=0 in
+// the environment sends them to the stream-K kernel instead (for comparison).
 bool pair_path_enabled() {
   static const bool on = [] {
     const char* e = getenv("B2_PAIR");
-    return e != nullptr && e[0] == '1';
+    return !(e != nullptr && e[0] == '0');
   }();
   return on;
 }
@@ -1717,14 +1710,6 @@ int max_resident_clusters(int S) {
 
 thread_local int g_last_gemm_path = 0;  // 0 = stream-K kernel, 1 = cluster kernel, 2 = CTA-pair kernel (set by launch_gemm)
 
-bool cluster_path_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("B2_CLUSTER");
-    return !(e != nullptr && e[0] == '0');
-  }();
-  return on;
-}
-
 // What launch_gemm decides for one problem, as data (the CPU tests read it through b2_plan_gemm).
 struct GemmPlan {
   int swap;           // 1 = feature-lane layout (weights on the 128-row side)
@@ -1735,17 +1720,6 @@ struct GemmPlan {
   int grid;           // CTAs launched
   int cluster_split;  // > 0: cluster kernel with this K split; 0: stream-K kernel
 };
-
-int twoshot_reducers() {
-  // B2_TWOSHOT_REDUCERS=n sets n CTAs aside that only reduce, following the GEMM's sweep over the rows, so
-  // that the second half of the NVLink traffic overlaps the tensor-core work.  Default 0: every CTA reduces
-  // after its GEMM work (SM time, not NVLink, bounds most shapes, and then setting CTAs aside only costs)
-  static const int reducers = [] {
-    const char* e = getenv("B2_TWOSHOT_REDUCERS");
-    return e != nullptr ? std::max(0, atoi(e)) : 0;
-  }();
-  return reducers;
-}
 
 // Picks the K split S of the cluster kernel for `tiles` output tiles of `kblocks` K blocks: the largest S that
 // keeps every cluster resident in one wave and leaves each CTA at least two K blocks.  0 = use the stream-K kernel.
@@ -1822,9 +1796,9 @@ int plan_gemm(int epi, int M, int N, int K, int num_sms, int min_grid, int reduc
 template <int EPI>
 int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K, GemmArgs& args,
                 int min_grid, cudaStream_t stream) {
-  const int reducers = EPI == EPI_PUSH2 ? twoshot_reducers() : 0;
+  const int reducers = 0;  // no CTAs are set aside for the reduce phase: every CTA reduces after its GEMM work
   GemmPlan plan;
-  const int prc = plan_gemm(EPI, M, N, K, ctx->num_sms, min_grid, reducers, ctx->tile_counter_cap, cluster_path_enabled(),
+  const int prc = plan_gemm(EPI, M, N, K, ctx->num_sms, min_grid, reducers, ctx->tile_counter_cap, true,
                             [](int bn, int S) {
                               if constexpr (EPI == EPI_PUSH2 || EPI == EPI_SAMPLE) return 0;
                               else return bn == 32 ? max_resident_clusters<32, EPI>(S) : max_resident_clusters<64, EPI>(S);
@@ -1843,7 +1817,6 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
   args.counters = ctx->tile_counters;
   args.status = ctx->status_dev;
   args.trace = ctx->trace_on ? ctx->trace : nullptr;
-  args.dedicated_reducers = reducers > 0 ? 1 : 0;
   args.gemm_ctas = plan.gemm_ctas;
   args.round_robin = plan.round_robin;
   const int grid = plan.grid;
@@ -1859,7 +1832,7 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
 
   g_last_gemm_path = 0;
   if constexpr (EPI == EPI_STORE || EPI == EPI_PUSH2) {
-    // CTA pairs (tcgen05.mma.cta_group::2) for many-token problems; opt-in until measured: B2_PAIR=1
+    // CTA pairs (tcgen05.mma.cta_group::2) for many-token problems: 1.1-1.2x the stream-K kernel from 512 tokens on
     if (pair_path_enabled() && !swap && bn >= 128 && M >= 512 && ctx->num_sms >= 2) {
       CUtensorMap tmQh;
       rc = b2::encode_tmap_2d(&tmQh, pQ, K, rowsQ, ldQ, BK, bn / 2);

@@ -3,7 +3,6 @@ the current CUDA stream, allocate outputs with torch and pass raw pointers."""
 from __future__ import annotations
 
 import ctypes as C
-import os
 
 import torch
 
@@ -63,10 +62,6 @@ def qkv_fused(x: torch.Tensor, w: torch.Tensor, bias, nq: int, nkv: int, head_di
     have_cache = k_cache is not None and k_cache.numel() > 0
     if have_cache:
         assert k_cache.stride(1) == nkv * head_dim and slot_mapping.dtype == torch.int32
-    if os.environ.get("B2_QKV_FUSED", "1") == "0":  # measurement switch: projection and head kernel as two calls
-        out = gemm(x2, w, bias)
-        qk_norm_rope_store(out, nq, nkv, head_dim, q_norm_w, k_norm_w, eps, positions, cos_sin, k_cache, v_cache, slot_mapping)
-        return out
     out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
     if M:
         _abi.check(_lib.b2_qkv_fused(get_runtime().ctx, x2.data_ptr(), x2.stride(0), w.data_ptr(), w.stride(0),

@@ -274,12 +274,12 @@ shutdown_runtime()
 """
 
 
-@pytest.mark.skipif(os.environ.get("B2_TEST_PAIR") != "1", reason="the CTA-pair GEMM is opt-in (B2_PAIR=1) until it has been measured; set B2_TEST_PAIR=1 to run it")
-def test_pair_kernel_opt_in():
-    """The tcgen05.mma.cta_group::2 kernel, in a child process whose environment switches it on."""
+def test_pair_kernel():
+    """The tcgen05.mma.cta_group::2 kernel (the default from 512 tokens on), in a child process of its own."""
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, B2_PAIR="1", MASTER_PORT="29547")
+    env = dict(os.environ, MASTER_PORT="29547")
+    env.pop("B2_PAIR", None)
     res = subprocess.run([sys.executable, "-c", PAIR_SCRIPT % {"root": root}], env=env, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
