@@ -202,7 +202,7 @@ int b2_gemm_static_scratch(const void* A, int64_t lda, const void* W, int64_t ld
  *              and sends the finished row and the new residual row to every
  *              rank: two NVLink store latencies and two system-scope fences,
  *              about 3 (world-1)/world M N 2 bytes sent per rank.  Used at
- *              world >= 4 for 65 .. min(1024, oneshot_tokens) tokens unless
+ *              world >= 4 for 65 .. min(1023, oneshot_tokens) tokens unless
  *              set otherwise with b2_ctx_set_option.  -0.0 in an output of
  *              this form is stored as +0.0. */
 int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias,
@@ -220,7 +220,7 @@ enum {
 };
 enum {
   B2_OPT_ROWPAR_FORM = 1,        /* B2_FORM_AUTO (default), _ONESHOT or _OWNER: what b2_rowpar_fused launches */
-  B2_OPT_OWNER_MAX_TOKENS = 2,   /* AUTO: largest M the row-owner form takes (default min(1024, oneshot_tokens)) */
+  B2_OPT_OWNER_MAX_TOKENS = 2,   /* AUTO: largest M the row-owner form takes (default min(1023, oneshot_tokens)) */
   B2_OPT_TWOSHOT_MIN_TOKENS = 3, /* b2_rowpar_form answers B2_FORM_TWOSHOT from this M on (default: the
                                     row-owner form's largest M + 1)                                            */
   B2_OPT_OWNER_MIN_TOKENS = 5,   /* AUTO: smallest M the row-owner form takes at world >= 4 (default 65: decode-

@@ -115,7 +115,7 @@ int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
   if (c->cfg.timeout_ms <= 0) c->cfg.timeout_ms = 5000;
   c->rowpar_form = B2_FORM_AUTO;
   c->owner_min_tokens = 65;
-  c->owner_max_tokens = std::min(1024, c->cfg.oneshot_tokens);
+  c->owner_max_tokens = std::min(1023, c->cfg.oneshot_tokens);  // from 1024 tokens on the two-shot form is as fast or faster
   c->twoshot_min_tokens = c->owner_max_tokens + 1;
   c->whole_tiles = true;
   const int rc = ctx_init(c);

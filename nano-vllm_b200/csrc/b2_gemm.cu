@@ -2250,6 +2250,18 @@ int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int6
   if (bias != nullptr && !aligned16(bias)) return B2_ERR_ARG;
   const int chunk = ctx->cfg.oneshot_tokens;
   const int world = ctx->cfg.world;
+  if (world == 1 && M > 64) {
+    // One rank, many tokens: nothing crosses a link, so the block is the plain GEMM (CTA pairs from 512 tokens on)
+    // followed by the HBM-bound add + RMSNorm kernel in place - two launches, both near their rooflines, instead of
+    // one whose reduce phase walks the rows one CTA at a time.
+    GemmArgs args{};
+    args.C = static_cast<uint16_t*>(normed_out);
+    args.ldc = N;
+    args.bias = static_cast<const uint16_t*>(bias);
+    rc = launch_gemm<EPI_STORE>(ctx, A, lda, W, ldw, M, N, Kr, args, 0, static_cast<cudaStream_t>(stream));
+    if (rc != B2_OK || norm_w == nullptr) return rc;
+    return b2_add_rmsnorm(normed_out, residual_in, norm_w, eps, M, N, normed_out, residual_out, stream);
+  }
   for (int m0 = 0; m0 < M; m0 += chunk) {
     const int m = std::min(chunk, M - m0);
     // the owner form when it is cheaper (or forced); every rank decides alike: the choice depends on M and the context only
