@@ -201,9 +201,10 @@ int b2_gemm_static_scratch(const void* A, int64_t lda, const void* W, int64_t ld
  *              go to their owner, which sums, adds the residual, normalises
  *              and sends the finished row and the new residual row to every
  *              rank: two NVLink store latencies and two system-scope fences,
- *              about 3 (world-1)/world M N 2 bytes sent per rank.  Used at
- *              world >= 4 for 65 .. min(1023, oneshot_tokens) tokens unless
- *              set otherwise with b2_ctx_set_option.  -0.0 in an output of
+ *              about 3 (world-1)/world M N 2 bytes sent per rank.  Used where
+ *              it was measured to win: Kr <= 6144 and 65 .. 1023 tokens at
+ *              world 8, 192 .. 511 tokens at world 4 (bounded by
+ *              oneshot_tokens), unless set otherwise with b2_ctx_set_option.  -0.0 in an output of
  *              this form is stored as +0.0. */
 int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias,
                     int M, int N, int Kr, const void* residual_in, const void* norm_w, float eps,
@@ -220,10 +221,10 @@ enum {
 };
 enum {
   B2_OPT_ROWPAR_FORM = 1,        /* B2_FORM_AUTO (default), _ONESHOT or _OWNER: what b2_rowpar_fused launches */
-  B2_OPT_OWNER_MAX_TOKENS = 2,   /* AUTO: largest M the row-owner form takes (default min(1023, oneshot_tokens)) */
+  B2_OPT_OWNER_MAX_TOKENS = 2,   /* AUTO: largest M the row-owner form takes (default 1023 at world 8, 511 at world 4, at most oneshot_tokens) */
   B2_OPT_TWOSHOT_MIN_TOKENS = 3, /* b2_rowpar_form answers B2_FORM_TWOSHOT from this M on (default: the
-                                    row-owner form's largest M + 1)                                            */
-  B2_OPT_OWNER_MIN_TOKENS = 5,   /* AUTO: smallest M the row-owner form takes at world >= 4 (default 65: decode-
+                                    row-owner form's largest M + 1 at world >= 4, 1025 at world 2)                                            */
+  B2_OPT_OWNER_MIN_TOKENS = 5,   /* AUTO: smallest M the row-owner form takes (default 65; 192 at world 4: decode-
                                     sized calls stay on the one-shot form)                                     */
   B2_OPT_WHOLE_TILES = 4         /* 1 (default): fused row-parallel calls with more than 64 tokens whose output tiles fit
                                     the SMs in one wave, and whose K is at most 6144, give every CTA one whole tile (no K split, no fp32

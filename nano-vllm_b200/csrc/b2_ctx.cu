@@ -115,8 +115,10 @@ int b2_ctx_create(const b2_config* cfg, b2_ctx** out) {
   if (c->cfg.timeout_ms <= 0) c->cfg.timeout_ms = 5000;
   c->rowpar_form = B2_FORM_AUTO;
   c->owner_min_tokens = 65;
-  c->owner_max_tokens = std::min(1023, c->cfg.oneshot_tokens);  // from 1024 tokens on the two-shot form is as fast or faster
-  c->twoshot_min_tokens = c->owner_max_tokens + 1;
+  // measured at Qwen3-32B shapes: the two-shot form takes over at 1024 tokens at 8 ranks and at 512 at 4 ranks; at 2 ranks
+  // the one-shot form (one copy either way) stays ahead up to its buffer's size
+  c->owner_max_tokens = std::min(c->cfg.world >= 8 ? 1023 : 511, c->cfg.oneshot_tokens);
+  c->twoshot_min_tokens = c->cfg.world >= 4 ? c->owner_max_tokens + 1 : std::min(1024, c->cfg.oneshot_tokens) + 1;
   c->whole_tiles = true;
   const int rc = ctx_init(c);
   if (rc != B2_OK) {

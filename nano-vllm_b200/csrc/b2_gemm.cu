@@ -2190,10 +2190,16 @@ int b2_rowpar_fused_twoshot(b2_ctx* ctx, const void* A, int64_t lda, const void*
 }
 
 // AUTO: the one-shot form for decode-sized calls (one NVLink store latency; its bytes are few) and at 1 or 2 ranks (one
-// copy to send either way); at 4 ranks and more the row-owner form from owner_min_tokens to owner_max_tokens tokens,
-// where sending every partial to every rank and reducing every row on every rank costs more than the second hop.
-static int auto_form(const b2_ctx* ctx, int m) {
-  return (ctx->cfg.world >= 4 && m >= ctx->owner_min_tokens && m <= ctx->owner_max_tokens) ? B2_FORM_OWNER : B2_FORM_ONESHOT;
+// copy to send either way).  At 4 ranks and more the row-owner form from owner_min_tokens to owner_max_tokens tokens,
+// where sending every partial to every rank and reducing every row on every rank costs more than the second hop and the
+// two fences - measured: from 65 tokens at 8 ranks, from 192 at 4 ranks, and only while the rank's K range is short
+// enough (<= 6144) for one whole tile per CTA; with a longer K the one-shot form stays ahead up to the two-shot range.
+static int auto_form(const b2_ctx* ctx, int m, int kr) {
+  const int world = ctx->cfg.world;
+  if (world < 4 || m < ctx->owner_min_tokens || m > ctx->owner_max_tokens) return B2_FORM_ONESHOT;
+  if ((kr + BK - 1) / BK > 96) return B2_FORM_ONESHOT;
+  if (world < 8 && m < 192) return B2_FORM_ONESHOT;
+  return B2_FORM_OWNER;
 }
 
 // Which form of the fused row-parallel block serves M tokens on this context (B2_FORM_*).
@@ -2201,7 +2207,7 @@ static int rowpar_form_for(const b2_ctx* ctx, int M, int N) {
   const int world = ctx->cfg.world;
   if (world >= 2 && M >= ctx->twoshot_min_tokens && N == ctx->cfg.hidden && M <= ctx->cfg.max_tokens) return B2_FORM_TWOSHOT;
   if (ctx->rowpar_form == B2_FORM_ONESHOT || ctx->rowpar_form == B2_FORM_OWNER) return ctx->rowpar_form;
-  return auto_form(ctx, M);
+  return auto_form(ctx, M, 0);  // (without K: the form for a short K range)
 }
 
 int b2_rowpar_form(b2_ctx* ctx, int M, int N) {
@@ -2266,7 +2272,7 @@ int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int6
     const int m = std::min(chunk, M - m0);
     // the owner form when it is cheaper (or forced); every rank decides alike: the choice depends on M and the context only
     int form = ctx->rowpar_form;
-    if (form == B2_FORM_AUTO) form = auto_form(ctx, m);
+    if (form == B2_FORM_AUTO) form = auto_form(ctx, m, Kr);
     GemmArgs args{};
     args.bias = (ctx->cfg.rank == 0) ? static_cast<const uint16_t*>(bias) : nullptr;  // bias enters the sum once
     args.world = world;

@@ -24,7 +24,8 @@ class TPRuntime:
         self.rank, self.world, self.device = rank, world, device
         self.vocab, self.max_seqs, self.hidden, self.max_tokens = vocab, max_seqs, hidden, max_tokens
         self.oneshot_tokens = min(oneshot_tokens if oneshot_tokens > 0 else 1024, max_tokens)
-        self.default_twoshot_min_tokens = min(1023, self.oneshot_tokens) + 1  # the library's default (b2_ctx_create)
+        # the library's default (b2_ctx_create)
+        self.default_twoshot_min_tokens = (min(1023 if world >= 8 else 511, self.oneshot_tokens) if world >= 4 else min(1024, self.oneshot_tokens)) + 1
         cfg = _abi.Config(rank, world, device, max_tokens, hidden, oneshot_tokens, vocab, max_seqs, timeout_ms)
         ctx = C.c_void_p()
         torch.cuda.set_device(device)
