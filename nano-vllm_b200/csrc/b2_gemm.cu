@@ -1071,7 +1071,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUt
 // dealt round-robin to the CTAs of the cluster, each CTA receives the other CTAs' parts of its groups
 // in its own shared memory, sums them after one cluster barrier, and writes its share of the output
 // as whole 256-byte token rows.  No global-memory round trip and no atomics on the critical path.
-// Feature-lane layout only (weights on the 128-row MMA side), one token tile (M <= BN).
+// Feature-lane layout only (weights on the 128-row MMA side); up to 256 tokens as token tiles of BN <= 64, one cluster each.
 // ---------------------------------------------------------------------------
 template <int BN>
 struct CfgCluster {
@@ -1111,7 +1111,11 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = static_cast<int>(b2::cluster_nctarank());
   const int crank = static_cast<int>(b2::cluster_ctarank());
-  const int tile = blockIdx.x / S;  // the output tile of this cluster: features [tile * 128, +128)
+  // the output tile of this cluster: features [tile * 128, +128) of the tokens [tok0, tok0 + BN); the token tiles of one
+  // feature tile belong to consecutive clusters, so that its weight tiles are read from DRAM once and from L2 after that
+  const int ct = blockIdx.x / S;
+  const int tile = ct / a.tilesQ;
+  const int tok0 = (ct - tile * a.tilesQ) * BN;
   const int KB = a.kblocks;
   const int kb_base = KB / S, kb_rem = KB % S;
   const int kb0 = crank * kb_base + min(crank, kb_rem);
@@ -1160,7 +1164,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
       b2::pdl_wait();
       stamp(a, 3);
       for (int i = 0; i < pre; ++i)
-        b2::tma_load_2d(smem_base + i * C::STAGE_BYTES + C::P_BYTES, &tmQ, bar_full + i * 8, (kb0 + i) * BK, 0, b2::kEvictLast);
+        b2::tma_load_2d(smem_base + i * C::STAGE_BYTES + C::P_BYTES, &tmQ, bar_full + i * 8, (kb0 + i) * BK, tok0, b2::kEvictLast);
       int stage = pre == STAGES ? 0 : pre;
       uint32_t phase = pre == STAGES ? 1 : 0;
       for (int i = pre; i < n_units; ++i) {
@@ -1169,7 +1173,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
         b2::mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
         const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
         b2::tma_load_2d(dst, &tmP, fb, (kb0 + i) * BK, tile * BM, b2::kEvictFirst);
-        b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, (kb0 + i) * BK, 0, b2::kEvictLast);
+        b2::tma_load_2d(dst + C::P_BYTES, &tmQ, fb, (kb0 + i) * BK, tok0, b2::kEvictLast);
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
@@ -1207,7 +1211,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
 #pragma unroll
       for (int i = 0; i < PRE_ROWS; ++i) {
         const int lt = (warp - 2) + 4 * i;
-        const int token = (((lt >> 2) * S + crank) << 2) + (lt & 3);
+        const int token = tok0 + (((lt >> 2) * S + crank) << 2) + (lt & 3);
         pre_slot[i] = -1;
         pre_cs[i][0] = pre_cs[i][1] = pre_cs[i][2] = pre_cs[i][3] = 0.f;
         if (token < a.M && (lt >> 2) * S + crank < C::GROUPS) {
@@ -1288,7 +1292,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
       for (int i = 0; i < 16; ++i) {  // at most 64 owned rows, 4 warps
         const int lt = (warp - 2) + 4 * i;
         if (lt >= owned * 4) break;
-        const int token = (((lt >> 2) * S + crank) << 2) + (lt & 3);
+        const int token = tok0 + (((lt >> 2) * S + crank) << 2) + (lt & 3);
         if (token >= a.M) continue;
         const uint16_t* row = out16 + lt * BM;
         uint32_t lo = *reinterpret_cast<const uint32_t*>(row + lane * 2);
@@ -1340,7 +1344,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_consta
     const int et = threadIdx.x - 64;
     for (int idx = et; idx < owned * 4 * 16; idx += 128) {
       const int lt = idx >> 4, piece = idx & 15;
-      const int token = (((lt >> 2) * S + crank) << 2) + (lt & 3);
+      const int token = tok0 + (((lt >> 2) * S + crank) << 2) + (lt & 3);
       const int feat = tile * BM + piece * 8;
       if (token < a.M && feat < a.N) {
         uint4 w = *reinterpret_cast<const uint4*>(out_buf + lt * (BM * 2) + piece * 16);
@@ -1789,6 +1793,24 @@ int plan_gemm(int epi, int M, int N, int K, int num_sms, int min_grid, int reduc
       p.gemm_ctas = p.tilesP * p.cluster_split;
       p.grid = p.gemm_ctas;
     }
+  } else if ((epi == EPI_STORE || epi == EPI_PUSH) && clusters_on && p.swap && M > 64) {
+    // 65..256 tokens: the cluster kernel over 64-token tiles when all (feature tile, token tile) pairs fit one wave -
+    // no fp32 combine through L2, which costs these few-microsecond problems more than the GEMM itself
+    const int tq64 = (M + 63) / 64;
+    const int64_t pairs = static_cast<int64_t>(p.tilesP) * tq64;
+    int split = 0;
+    if (pairs <= num_sms) split = pick_cluster_split(64, static_cast<int>(pairs), p.kblocks, num_sms, resident);
+    // a plain GEMM's CTAs wait for nobody, so its tiles need not be resident together: up to 4 waves of unsplit tiles
+    else if (epi == EPI_STORE && pairs <= 4 * static_cast<int64_t>(num_sms) && p.kblocks <= 48 && resident(64, 1) > 0) split = 1;
+    {
+      if (split > 0) {
+        p.bn = 64;
+        p.tilesQ = tq64;
+        p.cluster_split = split;
+        p.gemm_ctas = static_cast<int>(pairs) * split;
+        p.grid = p.gemm_ctas;
+      }
+    }
   }
   return B2_OK;
 }
@@ -1848,8 +1870,8 @@ int launch_gemm(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t 
   if constexpr (EPI == EPI_STORE || EPI == EPI_PUSH || EPI == EPI_PUSH3) {
     if (plan.cluster_split > 0) {
       g_last_gemm_path = 1;
-      if (bn == 32) return launch_cluster_inst<32, EPI>(tmP, tmQ, args, args.tilesP, plan.cluster_split, stream);
-      return launch_cluster_inst<64, EPI>(tmP, tmQ, args, args.tilesP, plan.cluster_split, stream);
+      if (bn == 32) return launch_cluster_inst<32, EPI>(tmP, tmQ, args, args.tilesP * args.tilesQ, plan.cluster_split, stream);
+      return launch_cluster_inst<64, EPI>(tmP, tmQ, args, args.tilesP * args.tilesQ, plan.cluster_split, stream);
     }
   }
   if constexpr (EPI == EPI_PUSH3) {
@@ -2446,7 +2468,7 @@ extern "C" int b2_plan_cta_units(const b2_gemm_plan* plan, int cta, int* units, 
   if (plan == nullptr || cta < 0 || cap < 0 || (cap > 0 && units == nullptr)) return -B2_ERR_ARG;
   if (plan->cluster_split > 0) {  // gemm_cluster_kernel: tile = cluster index, K blocks split evenly over the cluster
     const int S = plan->cluster_split, tile = cta / S, crank = cta % S;
-    if (tile >= plan->tiles_p) return 0;
+    if (tile >= plan->tiles_p * plan->tiles_q) return 0;
     const int base = plan->kblocks / S, rem = plan->kblocks % S;
     const int kb0 = crank * base + (crank < rem ? crank : rem);
     const int n = base + (crank < rem ? 1 : 0);

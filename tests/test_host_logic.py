@@ -55,7 +55,7 @@ def check_plan(abi, plan, m, n, k):
     assert plan.tiles_p * 128 >= rows_p > (plan.tiles_p - 1) * 128
     assert plan.tiles_q * plan.bn >= rows_q > (plan.tiles_q - 1) * plan.bn
     assert plan.kblocks * 64 >= k > (plan.kblocks - 1) * 64
-    assert 1 <= plan.gemm_ctas <= plan.grid <= SMS
+    assert 1 <= plan.gemm_ctas <= plan.grid and (plan.grid <= SMS or (plan.cluster_split == 1 and plan.grid <= 4 * SMS))
     seen = {}
     holders = {}
     for cta in range(plan.grid):
@@ -139,8 +139,18 @@ def test_planner_choices_for_the_decode_shapes(pkg):
     assert (p.swap, p.bn, p.round_robin, p.gemm_ctas) == (0, 256, 1, 148)
     rc, p = plan_gemm(_abi, EPI_STORE, 16, 64, 64)                # one unit: one CTA
     assert (p.gemm_ctas, p.grid) == (1, 1)
-    rc, p = plan_gemm(_abi, EPI_PUSH, 128, 64, 64)                # one-shot, stream-K kernel: one CTA has GEMM work, but
-    assert (p.cluster_split, p.gemm_ctas, p.grid) == (0, 1, 128)  # the launch keeps a CTA per token row for the reduce phase
+    rc, p = plan_gemm(_abi, EPI_PUSH, 300, 64, 64)                # one-shot, stream-K kernel: one CTA has GEMM work, but
+    assert (p.cluster_split, p.gemm_ctas, p.grid) == (0, 1, 148)  # the launch keeps CTAs for the reduce phase (one per row, at most all SMs)
+    rc, p = plan_gemm(_abi, EPI_STORE, 256, 4096, 1024)           # 65..256 tokens: 64-token tiles on the cluster kernel when every
+    assert (p.bn, p.tiles_p, p.tiles_q, p.cluster_split, p.grid) == (64, 32, 4, 1, 128)   # (feature tile, token tile) pair fits one wave
+    rc, p = plan_gemm(_abi, EPI_STORE, 128, 1024, 2048)
+    assert (p.bn, p.tiles_p, p.tiles_q, p.cluster_split, p.grid) == (64, 8, 2, 8, 128)
+    rc, p = plan_gemm(_abi, EPI_STORE, 256, 6144, 4096)           # 48 x 4 pairs do not fit one wave and K is long: stream-K as before
+    assert (p.bn, p.cluster_split) == (256, 0)
+    rc, p = plan_gemm(_abi, EPI_STORE, 256, 6144, 1024)           # short K: unsplit tiles in two waves (a plain GEMM's CTAs wait for nobody)
+    assert (p.bn, p.tiles_q, p.cluster_split, p.grid) == (64, 4, 1, 192)
+    rc, p = plan_gemm(_abi, EPI_PUSH, 256, 6144, 1024)            # a fused call's CTAs wait for each other: one wave or stream-K
+    assert p.cluster_split == 0
     rc, p = plan_gemm(_abi, EPI_PUSH, 64, 5120, 1024)             # one-shot at decode size: the cluster kernel reduces too
     assert (p.tiles_p, p.cluster_split, p.grid) == (40, 3, 120)
     rc, p = plan_gemm(_abi, EPI_PUSH3, 64, 4096, 512)             # row-owner form, o_proj of Qwen3-8B at 8 ranks: 32 tiles x split 4
@@ -188,6 +198,8 @@ def test_planner_property(epi, m, n8, k8, sms):
             seen.add((tile, kb))
     assert len(seen) == tiles * plan.kblocks
     assert plan.gemm_ctas <= plan.grid <= max(sms, plan.gemm_ctas)
+    if epi != EPI_STORE:
+        assert plan.grid <= sms or plan.cluster_split == 0   # launches whose CTAs wait for each other fit one wave
 
 
 def _golden(name):
