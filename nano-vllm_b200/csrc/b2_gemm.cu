@@ -1803,7 +1803,8 @@ int plan_gemm(int epi, int M, int N, int K, int num_sms, int min_grid, int reduc
     // a plain GEMM's CTAs wait for nobody, so its tiles need not be resident together: up to 4 waves of unsplit tiles
     else if (epi == EPI_STORE && pairs <= 4 * static_cast<int64_t>(num_sms) && p.kblocks <= 48 && resident(64, 1) > 0) split = 1;
     {
-      if (split > 0) {
+      // (only while a CTA's share of K stays short: with a long K range and no room to split it, stream-K over all SMs wins)
+      if (split > 0 && (p.kblocks + split - 1) / split <= 32) {
         p.bn = 64;
         p.tilesQ = tq64;
         p.cluster_split = split;
