@@ -37,9 +37,15 @@ METRIC = "qwen3_8b_decode_tokens_per_s"
 BATCH, PROMPT_LEN = 64, 1024
 SHAPE_8B = dict(hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128, intermediate=12288, n_layers=36, vocab=151936)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# dram__bytes_read.sum + dram__bytes_write.sum of one gate_up (+SiLU*mul) launch at TP=1 from the committed ncu summary
-# (profiles/), per tensor-parallel size; None = not captured
-NCU_TRAFFIC_BYTES = {1: 212.9e6}
+def ncu_traffic_bytes(tp: int):
+    """DRAM bytes per launch of the kernel the roofline leg times, from the ncu capture on record for this tensor-parallel
+    size (a small JSON beside the capture summaries); None where no capture exists."""
+    try:
+        table = json.load(open(os.path.join(ROOT, "profiles", "ncu_dram_traffic.json")))
+        entry = table.get(f"gate_up_silu_mul_m{BATCH}_n{2 * SHAPE_8B['intermediate'] // tp}_k{SHAPE_8B['hidden']}_tp{tp}")
+        return entry["bytes"] if entry else None
+    except Exception:
+        return None
 
 
 def workload(tp: int) -> dict:
@@ -270,7 +276,7 @@ def run_b200(args) -> None:
     achieved = alg_bytes / (k_us * 1e-6) / 1e9
     roofline = {"bound": "hbm", "kernel": f"{'gemm_kernel<64,SWAP,STORE> (stream-K)' if n_local // 128 > 148 else 'gemm_cluster_kernel<64,STORE>'} gate_up_proj + SiLU*mul, M={BATCH} N={n_local} K={SHAPE_8B['hidden']}", "achieved": achieved,
                 "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_kind": pk_kind + " (burst copy bandwidth)",
-                "us_per_launch": k_us, "algorithmic_bytes": alg_bytes, "traffic": NCU_TRAFFIC_BYTES.get(world)}
+                "us_per_launch": k_us, "algorithmic_bytes": alg_bytes, "traffic": ncu_traffic_bytes(world)}
     # the whole step against the HBM bound: weights of the rank + KV read at the mean context length
     c = SHAPE_8B
     w_bytes = 2.0 * (c["n_layers"] * (c["hidden"] * (c["n_heads"] + 2 * c["n_kv_heads"]) * c["head_dim"] + c["hidden"] * c["n_heads"] * c["head_dim"]

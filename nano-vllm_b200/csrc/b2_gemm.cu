@@ -2279,7 +2279,7 @@ int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int6
   if (bias != nullptr && !aligned16(bias)) return B2_ERR_ARG;
   const int chunk = ctx->cfg.oneshot_tokens;
   const int world = ctx->cfg.world;
-  if (world == 1 && M > 64) {
+  if (world == 1 && M > 64 && ctx->rowpar_form == B2_FORM_AUTO) {
     // One rank, many tokens: nothing crosses a link, so the block is the plain GEMM (CTA pairs from 512 tokens on)
     // followed by the HBM-bound add + RMSNorm kernel in place - two launches, both near their rooflines, instead of
     // one whose reduce phase walks the rows one CTA at a time.

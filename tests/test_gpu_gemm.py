@@ -215,6 +215,29 @@ def test_rowpar_owner_form_single_rank(ops, rt, m, k, n):
     assert_close_bf16(normed, exact_n, f"alternating forms {m}x{k}x{n}")
 
 
+@pytest.mark.parametrize("m,k,n", [(128, 2048, 1024), (256, 1024, 2048), (200, 512, 1024), (96, 3072, 1024)])
+def test_rowpar_oneshot_token_tiles_single_rank(ops, rt, m, k, n):
+    """65..256 tokens through the one-shot form on the cluster kernel's 64-token tiles (what 2 and 4 ranks run at these
+    sizes), forced on one rank, where the default would be the plain GEMM followed by the norm kernel."""
+    from nanovllm_b200 import _abi
+    xs, ws, residual, norm_w = O.rowpar_case(m, k, n, 1, seed=m + k + 1)
+    auto_n, auto_s = ops.rowpar_fused(xs[0].to(DEV), ws[0].to(DEV), None, residual.to(DEV), norm_w.to(DEV), 1e-6)
+    rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_ONESHOT)
+    try:
+        for _ in range(3):
+            normed, new_res = ops.rowpar_fused(xs[0].to(DEV), ws[0].to(DEV), None, residual.to(DEV), norm_w.to(DEV), 1e-6)
+        assert _abi.lib.b2_last_gemm_kernel() == 1, "expected the cluster kernel"
+        torch.cuda.synchronize()
+        rt.check_status()
+    finally:
+        rt.set_option(_abi.OPT_ROWPAR_FORM, _abi.FORM_AUTO)
+    exact_n, exact_s = O.fused_row_parallel_norm_exact(xs, ws, residual, norm_w, 1e-6)
+    assert_close_bf16(new_res, exact_s, f"one-shot token tiles residual {m}x{k}x{n}")
+    assert_close_bf16(normed, exact_n, f"one-shot token tiles normed {m}x{k}x{n}")
+    assert_close_bf16(auto_n, exact_n, f"GEMM + norm kernel normed {m}x{k}x{n}")
+    assert_close_bf16(auto_s, exact_s, f"GEMM + norm kernel residual {m}x{k}x{n}")
+
+
 def test_rowpar_plain_forward_and_bias(ops, rt):
     """norm_w = None is RowParallelLinear.forward: y = x W^T (+ bias)."""
     xs, ws, _, _ = O.rowpar_case(64, 1024, 1024, 1, seed=4)

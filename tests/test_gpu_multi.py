@@ -36,7 +36,7 @@ def _worker(rank: int, world: int, port: int):
         # ---- fused row-parallel block: shapes follow each other without a host sync ----
         if big:
             shapes = [(64, 4096, 4096), (1, 2048, 1024), (8, 8192, H), (64, 12288, 4096), (200, 1024, H), (512, 2048, 1024),
-                      (700, 1024, 2048), (64, 4096, 4096)]
+                      (700, 1024, 2048), (64, 4096, 4096), (128, 2048, 1024), (256, 2048, 2048), (96, 6144, 1024)]
         else:
             shapes = [(64, 2048, 1024), (1, 1024, 1024), (8, 2048, H), (200, 1024, H), (512, 1024, 1024), (64, 1024, 512)]
         results = []
