@@ -533,8 +533,8 @@ __device__ __forceinline__ void store_finished(const GemmArgs& a, unsigned int p
 
 template <int S, int FORM>
 __device__ __forceinline__ int reduce_rows(const GemmArgs& a, unsigned int parity, float* red, volatile int* gave_up) {
-  // vectors in flight together: G * S loads of 16 bytes (the owner form has few rows per rank: one deeper batch per row)
-  constexpr int G = S >= 8 ? (FORM == FORM_OWNER ? 3 : 2) : (S == 4 ? 3 : MAX_ROW_VECS);
+  // vectors in flight together: G * S loads of 16 bytes (a 4096-wide row at 8 ranks is one batch of 24 loads per thread)
+  constexpr int G = S >= 8 ? 3 : (S == 4 ? 3 : MAX_ROW_VECS);
   constexpr bool TWO = FORM == FORM_BLOCKS;
   const int nvec = a.N >> 3;
   const int tid = threadIdx.x;
