@@ -265,12 +265,29 @@ __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
   const int64_t first = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
   if (a.world == 1) {
-    for (int64_t i = first; i < total; i += step) {
-      const int m = static_cast<int>(i / vpr);
-      const int v = static_cast<int>(i - static_cast<int64_t>(m) * vpr);
-      int64_t row = a.ids[m] - a.vocab_start;
-      if (row < 0 || row >= a.vocab_end - a.vocab_start) row = 0;  // the reference would fault; stay in bounds
-      stg_v4(a.out + static_cast<int64_t>(m) * a.H + v * 8, ldg_v4(a.W + row * a.H + v * 8));
+    // four rows' vectors in flight per thread: the id load in front of every row read is a dependent load, so one
+    // item at a time leaves the memory system a quarter full
+    constexpr int U = 4;
+    const int64_t span = a.vocab_end - a.vocab_start;
+    for (int64_t i0 = first; i0 < total; i0 += step * U) {
+      int64_t off[U];
+      uint4 val[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = i0 + u * step;
+        off[u] = -1;
+        if (i < total) {
+          const int m = static_cast<int>(i / vpr);
+          const int v = static_cast<int>(i - static_cast<int64_t>(m) * vpr);
+          int64_t row = a.ids[m] - a.vocab_start;
+          if (row < 0 || row >= span) row = 0;  // the reference would fault; stay in bounds
+          off[u] = static_cast<int64_t>(m) * a.H + v * 8;
+          val[u] = ldg_v4(a.W + row * a.H + v * 8);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (off[u] >= 0) stg_v4(a.out + off[u], val[u]);
     }
     return;
   }
