@@ -202,6 +202,7 @@ class ModelRunner:
         gv["context_lens"].zero_()
         gv["context_lens"][:n] = ctx.context_lens
         gv["block_tables"][:n, :ctx.block_tables.size(1)] = ctx.block_tables
+        self._bt_rows = {}  # the graph's table no longer matches what _decode_graph_step last staged
         self.graphs[bs].replay()
         return gv["outputs"][:n]
 
@@ -214,6 +215,7 @@ class ModelRunner:
             self._stage = {k: torch.zeros(gv[k].shape, dtype=gv[k].dtype, pin_memory=True) for k in
                            ("input_ids", "positions", "slot_mapping", "context_lens", "block_tables")}
             self._stage_np = {k: v.numpy() for k, v in self._stage.items()}
+            self._bt_rows = {}  # row of the staged block table -> the blocks last copied into the graph's table for it
         return self._stage, self._stage_np
 
     @torch.inference_mode()
@@ -230,14 +232,24 @@ class ModelRunner:
         np_["context_lens"][n:bs] = 0          # padded rows attend to nothing ...
         np_["slot_mapping"][:n] = [s.block_table[(l - 1) // blk] * blk + (l - 1) % blk for s, l in zip(seqs, lens)]
         np_["slot_mapping"][n:bs] = -1         # ... and store nothing
-        width = max(len(s.block_table) for s in seqs)
+        # block tables change only when a sequence takes a new block (every 256 tokens) or the batch changes: rows are
+        # rewritten, and the table copied, only then
         bt = np_["block_tables"]
+        rows = self._bt_rows
+        width, dirty = 0, False
         for i, s in enumerate(seqs):
-            bt[i, :len(s.block_table)] = s.block_table
+            t = s.block_table
+            width = max(width, len(t))
+            key = tuple(t)
+            if rows.get(i) != key:
+                bt[i, :len(t)] = t
+                rows[i] = key
+                dirty = True
         gv = self.graph_vars
         for k in ("input_ids", "positions", "slot_mapping", "context_lens"):
             gv[k][:bs].copy_(stage[k][:bs], non_blocking=True)
-        gv["block_tables"][:n, :width].copy_(stage["block_tables"][:n, :width], non_blocking=True)
+        if dirty:
+            gv["block_tables"][:n, :width].copy_(stage["block_tables"][:n, :width], non_blocking=True)
         self.graphs[bs].replay()
         set_context(False)  # the LM head only needs to know this is not a prefill step
         return gv["outputs"][:n]
@@ -251,7 +263,9 @@ class ModelRunner:
         else:
             ids, pos = self.prepare_prefill(seqs, num_new) if is_prefill else self.prepare_decode(seqs)
             hidden = self.run_hidden(ids, pos, is_prefill)
-        picked = torch.zeros(len(seqs), dtype=torch.int64, device=self.device)
+        if getattr(self, "_picked", None) is None or self._picked.numel() < len(seqs):
+            self._picked = torch.zeros(max(len(seqs), self.max_num_seqs), dtype=torch.int64, device=self.device)
+        picked = self._picked[:len(seqs)]  # one buffer for every step: rank 0's sampler fills it, the broadcast hands it to the others
         if self.fused_sampler and len(seqs) <= FUSED_SAMPLER_MAX_ROWS:
             temps = None if temperatures is None else self._h2d(temperatures, torch.float32)
             self.model.sample_tokens(hidden, temps, self.sample_seed, out=picked)
@@ -359,6 +373,7 @@ class ResidentDecoder:
         gv["positions"][:n] = r._h2d([len(s) - 1 for s in seqs], torch.int64)
         gv["context_lens"][:n] = r._h2d([len(s) for s in seqs], torch.int32)
         gv["slot_mapping"][:n] = r._h2d([s.block_table[(len(s) - 1) // bs] * bs + (len(s) - 1) % bs for s in seqs], torch.int32)
+        r._bt_rows = {}  # the graph's table is rewritten here: _decode_graph_step must stage its rows again
         gv["block_tables"][:n].fill_(-1)  # columns past a sequence's own blocks: no room (the advance kernel freezes such a row)
         gv["block_tables"][:n, :width] = r._h2d([s.block_table + [-1] * (width - len(s.block_table)) for s in seqs], torch.int32)
         # replays until the first sequence has filled its last block: each replay stores the K/V of one more position
