@@ -196,7 +196,9 @@ int b2_gemm_static_scratch(const void* A, int64_t lda, const void* W, int64_t ld
  * and arithmetic (every rank ends up with all rows of both outputs):
  *   one-shot   every rank receives every rank's partial and reduces all rows
  *              itself: one NVLink store latency, (world-1) M N 2 bytes sent
- *              per rank.  Used for up to 64 tokens (decode) and on one rank.
+ *              per rank.  Used for up to 64 tokens (decode) everywhere, at
+ *              world 2 up to oneshot_tokens, and at world 4 / 8 wherever the
+ *              row-owner form is not.
  *   row-owner  token row t is reduced by rank t mod world only: partial rows
  *              go to their owner, which sums, adds the residual, normalises
  *              and sends the finished row and the new residual row to every
@@ -204,8 +206,11 @@ int b2_gemm_static_scratch(const void* A, int64_t lda, const void* W, int64_t ld
  *              about 3 (world-1)/world M N 2 bytes sent per rank.  Used where
  *              it was measured to win: Kr <= 6144 and 65 .. 1023 tokens at
  *              world 8, 192 .. 511 tokens at world 4 (bounded by
- *              oneshot_tokens), unless set otherwise with b2_ctx_set_option.  -0.0 in an output of
- *              this form is stored as +0.0. */
+ *              oneshot_tokens), unless set otherwise with b2_ctx_set_option.
+ *              -0.0 in an output of this form is stored as +0.0.
+ * On one rank with more than 64 tokens nothing crosses a link and the call
+ * runs as the plain GEMM followed by the add + RMSNorm kernel in place (two
+ * launches), unless a form is forced. */
 int b2_rowpar_fused(b2_ctx* ctx, const void* A, int64_t lda, const void* W, int64_t ldw, const void* bias,
                     int M, int N, int Kr, const void* residual_in, const void* norm_w, float eps,
                     void* normed_out, void* residual_out, void* stream);
@@ -221,14 +226,16 @@ enum {
 };
 enum {
   B2_OPT_ROWPAR_FORM = 1,        /* B2_FORM_AUTO (default), _ONESHOT or _OWNER: what b2_rowpar_fused launches */
-  B2_OPT_OWNER_MAX_TOKENS = 2,   /* AUTO: largest M the row-owner form takes (default 1023 at world 8, 511 at world 4, at most oneshot_tokens) */
+  B2_OPT_OWNER_MAX_TOKENS = 2,   /* AUTO: largest M the row-owner form takes (default 1023 at world 8,
+                                    511 at world 4, at most oneshot_tokens)                                */
   B2_OPT_TWOSHOT_MIN_TOKENS = 3, /* b2_rowpar_form answers B2_FORM_TWOSHOT from this M on (default: the
-                                    row-owner form's largest M + 1 at world >= 4, 1025 at world 2)                                            */
-  B2_OPT_OWNER_MIN_TOKENS = 5,   /* AUTO: smallest M the row-owner form takes (default 65; 192 at world 4: decode-
-                                    sized calls stay on the one-shot form)                                     */
-  B2_OPT_WHOLE_TILES = 4         /* 1 (default): fused row-parallel calls with more than 64 tokens whose output tiles fit
-                                    the SMs in one wave, and whose K is at most 6144, give every CTA one whole tile (no K split, no fp32
-                                    combine in L2); 0: always a stream-K split over all SMs                      */
+                                    row-owner form's largest M + 1 at world >= 4, 1025 at world 2)         */
+  B2_OPT_OWNER_MIN_TOKENS = 5,   /* AUTO: smallest M the row-owner form takes (default 65: decode-sized calls
+                                    stay on the one-shot form; at world 4 never below 192)                  */
+  B2_OPT_WHOLE_TILES = 4         /* 1 (default): fused row-parallel calls with more than 64 tokens whose output
+                                    tiles fit the SMs in one wave, and whose K is at most 6144, give every CTA
+                                    one whole tile (no K split, no fp32 combine in L2); 0: always a stream-K
+                                    split over all SMs                                                      */
 };
 int b2_ctx_set_option(b2_ctx* ctx, int option, int64_t value);
 /* Which entry point and form serve M rows of N features on this context:
