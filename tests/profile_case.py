@@ -10,6 +10,7 @@ cases:
   qkv_decode      qkv projection M=64, N=6144, K=4096 with q/k-norm + RoPE + KV scatter in its epilogue, 8 weight copies
   oproj_decode    fused row-parallel launch, M=64, N=4096, Kr=4096 (Qwen3-8B o_proj at TP=1), 8 weight copies
   gemm_prefill    GEMM M=4096, N=4096, K=4096
+  gemm_mid        GEMM M=256, N=4096, K=1024 (Qwen3-0.6B qkv at a 256-sequence decode step), 40 weight copies
   rowpar_decode   fused row-parallel launch, M=64, N=4096, Kr=12288 (Qwen3-8B down_proj at TP=1)
   rowpar_prefill  fused row-parallel launch, M=1024, N=5120, Kr=1024
   store_kvcache   paged-KV scatter, 16384 tokens x D=1024
@@ -49,8 +50,8 @@ def main():
     def rnd(*shape, scale=1.0):
         return (torch.randn(*shape, device=dev, generator=g) * scale).bfloat16()
 
-    if a.case in ("gemm_decode", "gemm_prefill"):
-        m, n, k, copies = (64, 24576, 4096, 4) if a.case == "gemm_decode" else (4096, 4096, 4096, 2)
+    if a.case in ("gemm_decode", "gemm_prefill", "gemm_mid"):
+        m, n, k, copies = {"gemm_decode": (64, 24576, 4096, 4), "gemm_prefill": (4096, 4096, 4096, 2), "gemm_mid": (256, 4096, 1024, 40)}[a.case]
         x, ws = rnd(m, k), [rnd(n, k, scale=0.02) for _ in range(copies)]
         call = lambda i: ops.gemm(x, ws[i % copies])
     elif a.case == "silu_decode":
